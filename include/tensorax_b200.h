@@ -1,0 +1,137 @@
+/*
+ * tensorax_b200 -- C ABI of the B200 (sm_100a) scaled-dot-product-attention forward path.
+ *
+ * The library is a drop-in for the raw-pointer launcher layer that tensorax's
+ * pybind11 dispatchers call (tensorax csrc/tensor_ops.h:170-194 and :234-237).
+ * Each entry point below names the reference declaration it replaces.  Argument
+ * order and meaning are the reference's; the differences are
+ *   - names carry a `tx_` prefix and have C linkage,
+ *   - every function returns 0 on success or a TX_ERR_* code instead of printing
+ *     and calling exit() (csrc/cuda/cuda_utils.cuh:6-14); tx_last_error() gives the
+ *     message of the calling thread's last failure,
+ *   - pointers are device pointers unless the name ends in `_host`.
+ * Tensors are contiguous row-major [batch, heads, seq, dim].  There is no CPU
+ * fallback: without a CUDA device every compute entry point fails with
+ * TX_ERR_NO_DEVICE.
+ */
+#ifndef TENSORAX_B200_H
+#define TENSORAX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TX_API __attribute__((visibility("default")))
+#else
+#define TX_API
+#endif
+
+enum {
+    TX_OK = 0,
+    TX_ERR_INVALID = 1,    /* bad shape / pointer / dtype combination (reference: std::runtime_error) */
+    TX_ERR_NO_DEVICE = 2,  /* no usable CUDA device */
+    TX_ERR_CUDA = 3,       /* a CUDA runtime or driver call failed */
+    TX_ERR_KERNEL = 4,     /* a kernel gave up on a bounded wait and reported it */
+    TX_ERR_UNSUPPORTED = 5
+};
+
+enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
+
+/* flags of tx_sdpa_desc */
+enum {
+    TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
+    TX_SDPA_P_IN_TMEM = 2    /* tensor-core kernel: keep P in tensor memory instead of shared memory */
+};
+
+/* Message of the last failure on the calling thread ("" if none). */
+TX_API const char *tx_last_error(void);
+TX_API int tx_version(void);
+
+/* ---- device memory helpers: reference csrc/cuda/tensor_cuda.cu:7-29
+ *      (cuda_is_available, cuda_malloc, cuda_free, cuda_memcpy_h2d, cuda_memcpy_d2h) */
+TX_API int tx_cuda_is_available(void);
+TX_API void *tx_cuda_malloc(size_t bytes);            /* NULL on failure */
+TX_API int tx_cuda_free(void *ptr);
+TX_API int tx_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes);
+TX_API int tx_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes);
+TX_API int tx_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes);
+TX_API int tx_cuda_synchronize(void);
+/* pinned host memory for callers that stream inputs (no reference counterpart) */
+TX_API void *tx_host_alloc_pinned(size_t bytes);
+TX_API int tx_host_free_pinned(void *ptr);
+
+/* ---- fp32 SDPA launchers: reference csrc/tensor_ops.h:170-188 and :192-194
+ *      (sdpa_naive_cuda, sdpa_tiled_cuda, sdpa_flash_cuda, sdpa_mma_cuda,
+ *       sdpa_optimized_flash_cuda; kernels csrc/cuda/kernels/attn.cu:135-1111,1564-1615).
+ *      Q [B,H,Sq,d_k], K [B,H,Sk,d_k], V [B,H,Sk,d_v], optional dense additive
+ *      mask [B,H,Sq,Sk] (NULL = none), out [B,H,Sq,d_v], all fp32 on the device.
+ *      Like the reference they return after the result is complete. */
+TX_API int tx_sdpa_naive_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                              float *out, int64_t batch_size, int64_t num_heads,
+                              int64_t seq_len_q, int64_t seq_len_k, int64_t d_k, int64_t d_v);
+TX_API int tx_sdpa_tiled_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                              float *out, int64_t batch_size, int64_t num_heads,
+                              int64_t seq_len_q, int64_t seq_len_k, int64_t d_k, int64_t d_v);
+TX_API int tx_sdpa_flash_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                              float *out, int64_t batch_size, int64_t num_heads,
+                              int64_t seq_len_q, int64_t seq_len_k, int64_t d_k, int64_t d_v);
+TX_API int tx_sdpa_optimized_flash_cuda(const float *Q, const float *K, const float *V,
+                                        const float *mask, float *out, int64_t batch_size,
+                                        int64_t num_heads, int64_t seq_len_q, int64_t seq_len_k,
+                                        int64_t d_k, int64_t d_v);
+TX_API int tx_sdpa_mma_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                            float *out, int64_t batch_size, int64_t num_heads,
+                            int64_t seq_len_q, int64_t seq_len_k, int64_t d_k, int64_t d_v);
+
+/* ---- fp16 tensor-core SDPA: reference csrc/tensor_ops.h:186-188 (sdpa_mma_fp16_cuda;
+ *      kernel csrc/cuda/kernels/attn.cu:1143-1521).  fp16 Q/K/V, fp32 out, no mask. */
+TX_API int tx_sdpa_mma_fp16_cuda(const void *Q_h, const void *K_h, const void *V_h, float *out,
+                                 int64_t batch_size, int64_t num_heads, int64_t seq_len_q,
+                                 int64_t seq_len_k, int64_t d_k, int64_t d_v);
+
+/* ---- fp32 -> fp16 cast: reference csrc/tensor_ops.h:190 (cast_f32_to_f16_cuda;
+ *      csrc/cuda/kernels/attn.cu:1523-1562).  Round-to-nearest-even; like the
+ *      reference it does not synchronise (stream order is enough). */
+TX_API int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size);
+
+/* ---- general form (no reference counterpart: the reference has no fp16+mask,
+ *      no implicit causal / key-length mask and no grouped K/V heads; its dense
+ *      mask forms cannot exist at S = 8192).  Asynchronous on `stream`. */
+typedef struct tx_sdpa_desc {
+    const void *q;            /* [batch, q_heads,  seq_q, d_k]  dtype */
+    const void *k;            /* [batch, kv_heads, seq_k, d_k]  dtype */
+    const void *v;            /* [batch, kv_heads, seq_k, d_v]  dtype */
+    const float *mask;        /* optional dense additive fp32 [batch, q_heads, seq_q, seq_k] */
+    const int32_t *kv_lens;   /* optional [batch] on the device: keys j >= kv_lens[b] are masked */
+    float *out;               /* [batch, q_heads, seq_q, d_v] fp32 */
+    int64_t batch, q_heads, kv_heads, seq_q, seq_k, d_k, d_v;
+    int32_t dtype;            /* TX_DTYPE_* of q, k, v */
+    int32_t causal;           /* nonzero: key j visible to query i iff j <= i */
+    int32_t flags;            /* TX_SDPA_* */
+    int32_t reserved;
+    void *stream;             /* cudaStream_t; NULL = default stream */
+} tx_sdpa_desc;
+
+/* Enqueue one forward pass.  Query head h reads K/V head h / (q_heads/kv_heads). */
+TX_API int tx_sdpa_forward(const tx_sdpa_desc *desc);
+/* Wait for `stream` and report a kernel-side failure (bounded wait ran out), if any. */
+TX_API int tx_sdpa_finish(void *stream);
+/* 1 if tx_sdpa_forward would run `desc` on the tcgen05 kernel, 0 if on CUDA cores. */
+TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
+/* How many kernels of this library have been launched by this process so far. */
+TX_API int64_t tx_kernel_launch_count(void);
+
+/* ---- host-buffer form (no reference counterpart): `desc` holds HOST pointers
+ *      (q, k, v, kv_lens, out; mask must be NULL).  Copies in, runs, copies out,
+ *      and returns when `out` is complete.  Device staging buffers are cached in
+ *      the library and reused between calls. */
+TX_API int tx_sdpa_forward_host(const tx_sdpa_desc *desc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENSORAX_B200_H */

@@ -1,0 +1,133 @@
+"""ctypes front end of the CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+Two shared objects live beside this file, both built by ``oracle/Makefile``:
+
+* ``liboracle.so`` -- the plain-C restatement of the reference CPU SDPA
+  (``oracle/sdpa_oracle.c``, which cites tensorax ``csrc/cpu/tensor_cpu.cpp:464-529``).
+* ``_ref/libtensorax_ref_cpu.so`` -- the reference's own ``sdpa_cpu`` compiled from
+  the reference checkout, when that build was possible.
+
+Nothing in the product package imports this module: it is used by the tests,
+by the smoke check and by the benchmark's CPU legs, always as the checker or
+as the CPU baseline, never as the thing being shipped or measured as "ours".
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_SO = os.path.join(_HERE, "liboracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libtensorax_ref_cpu.so")
+
+_i64 = ctypes.c_int64
+_fp = ctypes.c_void_p
+
+
+def build(with_ref: bool | None = None, ref_root: str = "/root/reference") -> None:
+    """Compile the checkers.  ``with_ref=None`` builds the reference copy only
+    when the reference checkout is present on this machine."""
+    subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
+    if with_ref is None:
+        with_ref = os.path.isfile(os.path.join(ref_root, "csrc", "cpu", "tensor_cpu.cpp"))
+    if with_ref:
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True,
+                       capture_output=True)
+
+
+_lib = None
+_ref = None
+
+
+def _oracle():
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(_ORACLE_SO):
+            build(with_ref=False)
+        _lib = ctypes.CDLL(_ORACLE_SO)
+        _lib.oracle_sdpa_f32.argtypes = [_fp] * 5 + [_i64] * 6
+        _lib.oracle_sdpa_f32.restype = None
+        _lib.oracle_sdpa_structured.argtypes = (
+            [_fp] * 4 + [_i64] * 7 + [ctypes.c_int, _fp] + [_i64] * 4)
+        _lib.oracle_sdpa_structured.restype = None
+    return _lib
+
+
+def have_reference() -> bool:
+    return os.path.isfile(_REF_SO)
+
+
+def _reference():
+    global _ref
+    if _ref is None:
+        _ref = ctypes.CDLL(_REF_SO)
+        _ref.ref_sdpa_cpu.argtypes = [_fp] * 5 + [_i64] * 6
+        _ref.ref_sdpa_cpu.restype = None
+    return _ref
+
+
+def _f32c(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _dense(fn, q, k, v, mask):
+    q, k, v = _f32c(q), _f32c(k), _f32c(v)
+    B, H, Sq, dk = q.shape
+    Sk, dv = k.shape[2], v.shape[3]
+    m = None if mask is None else _f32c(mask)
+    if m is not None:
+        assert m.shape == (B, H, Sq, Sk), "dense mask must be [B,H,Sq,Sk] as the reference requires"
+    out = np.empty((B, H, Sq, dv), dtype=np.float32)
+    fn(_ptr(q), _ptr(k), _ptr(v), _ptr(m), _ptr(out), B, H, Sq, Sk, dk, dv)
+    return out
+
+
+def sdpa_f32(q, k, v, mask=None):
+    """Restated oracle, same contract as the reference ``sdpa_cpu``."""
+    return _dense(_oracle().oracle_sdpa_f32, q, k, v, mask)
+
+
+def ref_sdpa_cpu(q, k, v, mask=None):
+    """The reference's own ``sdpa_cpu`` (only where ``have_reference()``)."""
+    return _dense(_reference().ref_sdpa_cpu, q, k, v, mask)
+
+
+def sdpa_structured(q, k, v, causal=False, kv_lens=None, heads=None, rows=None, out=None,
+                    threads: int = 1):
+    """Oracle with implicit causal / key-length masks and grouped K/V heads.
+
+    q: [B,Hq,Sq,dk]; k: [B,Hkv,Sk,dk]; v: [B,Hkv,Sk,dv] (any float dtype, widened
+    to fp32 exactly).  ``heads`` = iterable of flattened b*Hq+h indices to evaluate
+    (default all), ``rows`` = (begin, end) query-row range (default all).  Rows that
+    are not evaluated are left as NaN in the returned array.
+    """
+    q, k, v = _f32c(q), _f32c(k), _f32c(v)
+    B, Hq, Sq, dk = q.shape
+    Hkv, Sk, dv = k.shape[1], k.shape[2], v.shape[3]
+    assert Hq % Hkv == 0
+    lens = None if kv_lens is None else np.ascontiguousarray(kv_lens, dtype=np.int32)
+    if out is None:
+        out = np.full((B, Hq, Sq, dv), np.nan, dtype=np.float32)
+    r0, r1 = (0, Sq) if rows is None else rows
+    head_list = list(range(B * Hq)) if heads is None else list(heads)
+    lib = _oracle()
+
+    def one(bh):
+        lib.oracle_sdpa_structured(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, Hq, Hkv, Sq, Sk, dk,
+                                   dv, int(bool(causal)), _ptr(lens), bh, bh + 1, r0, r1)
+
+    if threads <= 1 or len(head_list) <= 1:
+        for bh in head_list:
+            one(bh)
+    else:
+        with ThreadPoolExecutor(max_workers=threads) as ex:
+            list(ex.map(one, head_list))
+    return out

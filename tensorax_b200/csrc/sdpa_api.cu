@@ -1,0 +1,478 @@
+// C ABI of the B200 SDPA forward path: validation, kernel selection, launch.
+// Declarations and the reference interfaces they replace: include/tensorax_b200.h.
+#include "../../include/tensorax_b200.h"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "sdpa_simt.cuh"
+#include "sdpa_tc.cuh"
+
+namespace {
+
+thread_local std::string g_err;
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define TX_CUDA(call)                                                                     \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess)                                                            \
+            return fail(TX_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_));     \
+    } while (0)
+
+int ensure_device()
+{
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return fail(TX_ERR_NO_DEVICE, "no CUDA device available (%s)",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    }
+    return TX_OK;
+}
+
+// One status word per device, written by kernels whose bounded waits run out.
+constexpr int kMaxDevices = 64;
+int *g_status[kMaxDevices] = {};
+std::mutex g_status_mu;
+
+int status_word(int **out)
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TX_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    if (!g_status[dev]) {
+        int *w = nullptr;
+        TX_CUDA(cudaMalloc(&w, 256));
+        TX_CUDA(cudaMemset(w, 0, 256));
+        g_status[dev] = w;
+    }
+    *out = g_status[dev];
+    return TX_OK;
+}
+
+// ------------------------------------------------------------------ TMA descriptors
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn *fn)
+{
+    static EncodeTiledFn cached = nullptr;
+    if (!cached) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        TX_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
+        if (!sym || q != cudaDriverEntryPointSuccess)
+            return fail(TX_ERR_CUDA, "driver does not provide cuTensorMapEncodeTiled");
+        cached = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    *fn = cached;
+    return TX_OK;
+}
+
+// fp16 tensor [slabs, rows, d] -> 3-D map (d, rows, slabs); box = 64 columns x box_rows, 128B swizzle.
+int make_map(CUtensorMap *m, const void *base, int64_t slabs, int64_t rows, int64_t d, int box_rows)
+{
+    EncodeTiledFn enc;
+    if (int rc = get_encode_fn(&enc)) return rc;
+    cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)slabs};
+    cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)rows * (cuuint64_t)d * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TX_OK;
+}
+
+// ------------------------------------------------------------------ validation
+int validate(const tx_sdpa_desc *d)
+{
+    if (!d) return fail(TX_ERR_INVALID, "SDPA: null descriptor");
+    if (!d->q || !d->k || !d->v || !d->out)
+        return fail(TX_ERR_INVALID, "SDPA: Query, Key, Value and output pointers must not be null");
+    if (d->batch <= 0 || d->q_heads <= 0 || d->kv_heads <= 0 || d->seq_q <= 0 || d->seq_k <= 0 ||
+        d->d_k <= 0 || d->d_v <= 0)
+        return fail(TX_ERR_INVALID, "SDPA: every dimension must be positive");
+    if (d->q_heads % d->kv_heads != 0)
+        return fail(TX_ERR_INVALID, "SDPA: Key dimensions don't match Query (q_heads %lld not a multiple of kv_heads %lld)",
+                    (long long)d->q_heads, (long long)d->kv_heads);
+    if (d->dtype != TX_DTYPE_F32 && d->dtype != TX_DTYPE_F16)
+        return fail(TX_ERR_INVALID, "SDPA: dtype must be float32 or float16");
+    if (d->batch * d->q_heads > 0x7fffffffLL / 2 || d->seq_q > 0x3fffffffLL || d->seq_k > 0x3fffffffLL)
+        return fail(TX_ERR_UNSUPPORTED, "SDPA: dimension too large");
+    return TX_OK;
+}
+
+bool tc_eligible(const tx_sdpa_desc *d)
+{
+    if (d->flags & TX_SDPA_FORCE_SIMT) return false;
+    if (d->dtype != TX_DTYPE_F16 || d->mask) return false;
+    if (d->d_k != d->d_v || (d->d_k != 64 && d->d_k != 128)) return false;
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al(d->q) || !al(d->k) || !al(d->v) || !al(d->out)) return false;
+    if (d->batch * d->q_heads > 65535) return false;   // grid.y
+    return true;
+}
+
+// ------------------------------------------------------------------ launches
+template <typename T, int DVC>
+int launch_simt_t(const txb::SimtParams &p, cudaStream_t st)
+{
+    dim3 grid((unsigned)((p.dv + 32 * DVC - 1) / (32 * DVC)),
+              (unsigned)((p.Sq + txb::SIMT_BR - 1) / txb::SIMT_BR), (unsigned)(p.B * p.Hq));
+    txb::sdpa_simt_kernel<T, DVC><<<grid, txb::SIMT_THREADS, 0, st>>>(p);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+template <typename T>
+int launch_simt(const txb::SimtParams &p, cudaStream_t st)
+{
+    if (p.B * p.Hq > 65535) return fail(TX_ERR_UNSUPPORTED, "SDPA: batch*heads > 65535");
+    if ((p.Sq + txb::SIMT_BR - 1) / txb::SIMT_BR > 65535) return fail(TX_ERR_UNSUPPORTED, "SDPA: seq_len_q too large");
+    if (p.dv <= 32) return launch_simt_t<T, 1>(p, st);
+    if (p.dv <= 64) return launch_simt_t<T, 2>(p, st);
+    if (p.dv <= 128) return launch_simt_t<T, 4>(p, st);
+    return launch_simt_t<T, 8>(p, st);   // wider heads: one CTA column per 256 value columns
+}
+
+template <class Cfg>
+int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+{
+    CUtensorMap tq, tk, tv;
+    if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, d->d_k, Cfg::BM)) return rc;
+    if (int rc = make_map(&tk, d->k, d->batch * d->kv_heads, d->seq_k, d->d_k, Cfg::BN)) return rc;
+    if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, d->d_v, Cfg::BN)) return rc;
+    txb::TcParams p;
+    p.out = d->out;
+    p.kv_lens = d->kv_lens;
+    p.status = status;
+    p.Hq = (int)d->q_heads;
+    p.Hkv = (int)d->kv_heads;
+    p.Sq = (int)d->seq_q;
+    p.Sk = (int)d->seq_k;
+    p.causal = d->causal ? 1 : 0;
+    p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
+    static bool attr_set = false;   // per template instantiation
+    if (!attr_set) {
+        TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads));
+    txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+{
+    const bool ptm = (d->flags & TX_SDPA_P_IN_TMEM) != 0;
+    if (d->d_k == 64) {
+        if (ptm) return launch_tc_t<txb::TcCfg<64, 128, 2, true>>(d, st, status);
+        return launch_tc_t<txb::TcCfg<64, 128, 2, false>>(d, st, status);
+    }
+    if (ptm) return launch_tc_t<txb::TcCfg<128, 64, 2, true>>(d, st, status);
+    return launch_tc_t<txb::TcCfg<128, 64, 2, false>>(d, st, status);
+}
+
+int forward(const tx_sdpa_desc *d)
+{
+    if (int rc = validate(d)) return rc;
+    if (int rc = ensure_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(d->stream);
+    if (tc_eligible(d)) {
+        int *status = nullptr;
+        if (int rc = status_word(&status)) return rc;
+        return launch_tc(d, st, status);
+    }
+    txb::SimtParams p;
+    p.q = d->q; p.k = d->k; p.v = d->v;
+    p.mask = d->mask;
+    p.kv_lens = d->kv_lens;
+    p.out = d->out;
+    p.B = d->batch; p.Hq = d->q_heads; p.Hkv = d->kv_heads;
+    p.Sq = d->seq_q; p.Sk = d->seq_k; p.dk = d->d_k; p.dv = d->d_v;
+    p.causal = d->causal ? 1 : 0;
+    p.scale = 1.0f / std::sqrt((float)d->d_k);
+    return d->dtype == TX_DTYPE_F16 ? launch_simt<__half>(p, st) : launch_simt<float>(p, st);
+}
+
+int finish(cudaStream_t st)
+{
+    TX_CUDA(cudaStreamSynchronize(st));
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    int *w = (dev >= 0 && dev < kMaxDevices) ? g_status[dev] : nullptr;
+    if (w) {
+        int code = 0;
+        TX_CUDA(cudaMemcpy(&code, w, sizeof code, cudaMemcpyDeviceToHost));
+        if (code != 0) {
+            (void)cudaMemset(w, 0, sizeof code);
+            return fail(TX_ERR_KERNEL, "SDPA kernel gave up on a bounded wait (stage code %d); output is not valid", code);
+        }
+    }
+    return TX_OK;
+}
+
+int sync_f32(const float *Q, const float *K, const float *V, const float *mask, float *out,
+             int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    tx_sdpa_desc d;
+    std::memset(&d, 0, sizeof d);
+    d.q = Q; d.k = K; d.v = V; d.mask = mask; d.out = out;
+    d.batch = B; d.q_heads = H; d.kv_heads = H; d.seq_q = Sq; d.seq_k = Sk; d.d_k = dk; d.d_v = dv;
+    d.dtype = TX_DTYPE_F32;
+    if (int rc = forward(&d)) return rc;
+    return finish(nullptr);
+}
+
+__global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n)
+{
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        const float4 f = *reinterpret_cast<const float4 *>(in + i);
+        __half2 a = __floats2half2_rn(f.x, f.y), b = __floats2half2_rn(f.z, f.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t *>(&a);
+        u.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(out + i) = u;
+    } else {
+        for (int64_t j = i; j < n && j < i + 4; ++j) out[j] = __float2half_rn(in[j]);
+    }
+}
+
+// ------------------------------------------------------------------ host-buffer form
+struct Workspace {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+Workspace g_ws[kMaxDevices];
+std::mutex g_ws_mu;
+
+int workspace(size_t bytes, void **out)
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TX_ERR_INVALID, "device index %d out of range", dev);
+    Workspace &w = g_ws[dev];
+    if (w.bytes < bytes) {
+        if (w.ptr) TX_CUDA(cudaFree(w.ptr));
+        w.ptr = nullptr;
+        w.bytes = 0;
+        TX_CUDA(cudaMalloc(&w.ptr, bytes));
+        w.bytes = bytes;
+    }
+    *out = w.ptr;
+    return TX_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+const char *tx_last_error(void) { return g_err.c_str(); }
+int tx_version(void) { return 100; }
+
+int tx_cuda_is_available(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n > 0 ? 1 : 0;
+}
+
+void *tx_cuda_malloc(size_t bytes)
+{
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess) {
+        fail(TX_ERR_CUDA, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+int tx_cuda_free(void *ptr)
+{
+    if (!ptr) return TX_OK;
+    TX_CUDA(cudaFree(ptr));
+    return TX_OK;
+}
+
+int tx_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes)
+{
+    TX_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    return TX_OK;
+}
+
+int tx_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes)
+{
+    TX_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    return TX_OK;
+}
+
+int tx_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes)
+{
+    TX_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice));
+    return TX_OK;
+}
+
+int tx_cuda_synchronize(void)
+{
+    TX_CUDA(cudaDeviceSynchronize());
+    return TX_OK;
+}
+
+void *tx_host_alloc_pinned(size_t bytes)
+{
+    void *p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        fail(TX_ERR_CUDA, "cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+int tx_host_free_pinned(void *ptr)
+{
+    if (!ptr) return TX_OK;
+    TX_CUDA(cudaFreeHost(ptr));
+    return TX_OK;
+}
+
+int tx_sdpa_naive_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+                       int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
+}
+int tx_sdpa_tiled_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+                       int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
+}
+int tx_sdpa_flash_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+                       int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
+}
+int tx_sdpa_optimized_flash_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                                 float *out, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk,
+                                 int64_t dv)
+{
+    return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
+}
+int tx_sdpa_mma_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+                     int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    // The reference computes this variant with fp16 operands; the exact-fp32 kernel
+    // is used here, which is strictly closer to the CPU path.
+    return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
+}
+
+int tx_sdpa_mma_fp16_cuda(const void *Q_h, const void *K_h, const void *V_h, float *out, int64_t B,
+                          int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
+{
+    tx_sdpa_desc d;
+    std::memset(&d, 0, sizeof d);
+    d.q = Q_h; d.k = K_h; d.v = V_h; d.out = out;
+    d.batch = B; d.q_heads = H; d.kv_heads = H; d.seq_q = Sq; d.seq_k = Sk; d.d_k = dk; d.d_v = dv;
+    d.dtype = TX_DTYPE_F16;
+    if (int rc = forward(&d)) return rc;
+    return finish(nullptr);
+}
+
+int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size)
+{
+    if (size < 0 || (size > 0 && (!in || !out))) return fail(TX_ERR_INVALID, "cast_to_fp16: bad arguments");
+    if (int rc = ensure_device()) return rc;
+    if (size == 0) return TX_OK;
+    const int threads = 256;
+    const int64_t blocks = (size + threads * 4 - 1) / (threads * 4);
+    if (blocks > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "cast_to_fp16: tensor too large");
+    cast_f32_to_f16_kernel<<<(unsigned)blocks, threads>>>(in, static_cast<__half *>(out), size);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+int tx_sdpa_forward(const tx_sdpa_desc *desc) { return forward(desc); }
+
+int tx_sdpa_finish(void *stream) { return finish(static_cast<cudaStream_t>(stream)); }
+
+int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc)
+{
+    if (validate(desc) != TX_OK) return 0;
+    return tc_eligible(desc) ? 1 : 0;
+}
+
+int64_t tx_kernel_launch_count(void) { return g_launches.load(); }
+
+int tx_sdpa_forward_host(const tx_sdpa_desc *h)
+{
+    if (int rc = validate(h)) return rc;
+    if (h->mask) return fail(TX_ERR_UNSUPPORTED, "SDPA host form: dense masks are not taken; use causal / kv_lens");
+    if (int rc = ensure_device()) return rc;
+    const size_t es = h->dtype == TX_DTYPE_F16 ? 2 : 4;
+    const size_t nq = (size_t)(h->batch * h->q_heads * h->seq_q * h->d_k) * es;
+    const size_t nk = (size_t)(h->batch * h->kv_heads * h->seq_k * h->d_k) * es;
+    const size_t nv = (size_t)(h->batch * h->kv_heads * h->seq_k * h->d_v) * es;
+    const size_t no = (size_t)(h->batch * h->q_heads * h->seq_q * h->d_v) * 4;
+    const size_t nl = h->kv_lens ? (size_t)h->batch * 4 : 0;
+    const size_t oq = 0, ok = align_up(oq + nq, 256), ov = align_up(ok + nk, 256),
+                 oo = align_up(ov + nv, 256), ol = align_up(oo + no, 256);
+    const size_t total = align_up(ol + nl, 256);
+    std::lock_guard<std::mutex> lk(g_ws_mu);
+    void *base = nullptr;
+    if (int rc = workspace(total, &base)) return rc;
+    char *w = static_cast<char *>(base);
+    cudaStream_t st = static_cast<cudaStream_t>(h->stream);
+    TX_CUDA(cudaMemcpyAsync(w + oq, h->q, nq, cudaMemcpyHostToDevice, st));
+    TX_CUDA(cudaMemcpyAsync(w + ok, h->k, nk, cudaMemcpyHostToDevice, st));
+    TX_CUDA(cudaMemcpyAsync(w + ov, h->v, nv, cudaMemcpyHostToDevice, st));
+    if (nl) TX_CUDA(cudaMemcpyAsync(w + ol, h->kv_lens, nl, cudaMemcpyHostToDevice, st));
+    tx_sdpa_desc d = *h;
+    d.q = w + oq; d.k = w + ok; d.v = w + ov;
+    d.out = reinterpret_cast<float *>(w + oo);
+    d.kv_lens = nl ? reinterpret_cast<const int32_t *>(w + ol) : nullptr;
+    if (int rc = forward(&d)) return rc;
+    TX_CUDA(cudaMemcpyAsync(h->out, w + oo, no, cudaMemcpyDeviceToHost, st));
+    return finish(st);
+}
+
+}  // extern "C"

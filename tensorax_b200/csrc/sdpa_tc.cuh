@@ -1,0 +1,390 @@
+// fp16 flash-attention forward for sm_100a: TMA-staged Q/K/V tiles, QK^T and PV
+// as tcgen05 MMAs accumulating in tensor memory, fp32 online softmax.
+//
+// Replaces the reference's fp16 tensor-core path (tensorax
+// csrc/cuda/kernels/attn.cu:1143-1521, sdpa_kernel_mma_fp16 + sdpa_mma_fp16_cuda):
+// fp16 Q/K/V [B,H,S,d] -> fp32 O, fp32 accumulation, P rounded to fp16 before PV
+// (attn.cu:1357-1360).  Differences on purpose: the softmax scale is applied in
+// fp32 inside the exponent instead of pre-multiplying Q in fp16 (attn.cu:1218-1232),
+// and causal / key-length masks and grouped K/V heads are applied in-kernel,
+// which the reference path cannot do at all.
+//
+// One CTA = one 128-row query tile of one (batch, query head).  Six warps:
+//   warp 0      TMA producer (one lane): Q once, then K/V tiles through an
+//               NS-deep ring of shared-memory stages, 128-byte swizzled
+//   warp 1      owns tensor memory (alloc/dealloc); one lane issues every MMA:
+//               S = Q K^T (M=128, N=BN, K=16 per instruction) and
+//               O += P V  (M=128, N=D,  K=16 per instruction, V read MN-major)
+//   warps 2-5   softmax: thread t owns query row 32*(warp%4)+lane, the tensor
+//               memory lane it is allowed to read.  Two passes over S in
+//               32-column chunks (row max, then exp2 + fp16 pack), O rescaled in
+//               tensor memory only when the running max grew by more than 2^8,
+//               masks applied in registers, epilogue O/l -> global fp32.
+// Two such CTAs fit one SM (shared memory <= 113 KB, 256 tensor-memory columns,
+// <= 168 registers), so one CTA's softmax overlaps the other's MMAs.
+//
+// Every mbarrier wait is bounded; a wait that runs out records a code in
+// `status` and the whole CTA drains and frees its tensor memory.
+#pragma once
+#include "ptx.cuh"
+
+namespace txb {
+
+struct TcParams {
+    float *out;               // [B,Hq,Sq,D] fp32
+    const int32_t *kv_lens;   // optional [B]
+    int *status;              // device word: 0 = ok, else first failing wait's code
+    int Hq, Hkv, Sq, Sk;
+    int causal;
+    float scale_log2;         // (1/sqrt(d)) * log2(e)
+};
+
+enum TcStatus : int {
+    TC_OK = 0,
+    TC_ERR_ALIGN = 1,
+    TC_ERR_PRODUCER = 2,
+    TC_ERR_MMA = 3,
+    TC_ERR_SOFTMAX = 4,
+};
+
+template <int D_, int BN_, int NS_, bool P_TMEM_>
+struct TcCfg {
+    static constexpr int D = D_;          // head dim (d_k == d_v)
+    static constexpr int BN = BN_;        // keys per tile
+    static constexpr int NS = NS_;        // K/V ring depth
+    static constexpr bool P_TMEM = P_TMEM_;
+    static constexpr int BM = 128;        // query rows per CTA
+    static constexpr int THREADS = 192;
+    static constexpr int DP = D / 64;     // 64-column (128-byte) panels per row of Q/K/V
+    static constexpr int NP = BN / 64;    // panels per row of P
+    static constexpr uint32_t Q_BYTES = BM * D * 2;
+    static constexpr uint32_t KV_BYTES = BN * D * 2;       // one K or V stage
+    static constexpr uint32_t KV_PANEL = BN * 128;         // one 64-column panel of a stage
+    static constexpr uint32_t P_BYTES = P_TMEM ? 0 : BM * BN * 2;
+    static constexpr uint32_t OFF_Q = 0;
+    static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
+    static constexpr uint32_t OFF_V = OFF_K + NS * KV_BYTES;
+    static constexpr uint32_t OFF_P = OFF_V + NS * KV_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
+    // barriers: q_full, s_full, s_free, p_full, pv_done, then k_full/k_empty/v_full/v_empty[NS]
+    static constexpr int N_BARS = 5 + 4 * NS;
+    static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
+    static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
+    static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
+    // tensor memory columns: S fp32 [BN] | O fp32 [D] | P fp16 pairs [BN/2] (only if P_TMEM)
+    static constexpr uint32_t COL_S = 0;
+    static constexpr uint32_t COL_O = BN;
+    static constexpr uint32_t COL_P = BN + D;
+    static constexpr uint32_t COLS_USED = BN + D + (P_TMEM ? BN / 2 : 0);
+    static constexpr uint32_t TMEM_COLS = COLS_USED <= 32 ? 32 : COLS_USED <= 64 ? 64
+                                        : COLS_USED <= 128 ? 128 : COLS_USED <= 256 ? 256 : 512;
+    static_assert(D % 64 == 0 && BN % 64 == 0, "panels are 64 columns wide");
+    static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
+    static_assert(BN <= 256 && D <= 256, "one MMA instruction covers N <= 256");
+};
+
+// Running-max growth (in log2 units) tolerated before O and l are rescaled.
+// P then stays below 2^8, far inside fp16 range, and the final O/l is exact.
+constexpr float kLazyRescaleLog2 = 8.0f;
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, (Cfg::SMEM_BYTES <= 115712 && Cfg::TMEM_COLS <= 256) ? 2 : 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const TcParams p)
+{
+    constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const uint32_t q_s = sbase + Cfg::OFF_Q, k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V;
+    const uint32_t p_s = sbase + Cfg::OFF_P;
+    const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+    const uint32_t q_full = bar0, s_full = bar0 + 8, s_free = bar0 + 16, p_full = bar0 + 24,
+                   pv_done = bar0 + 32;
+    const uint32_t k_full = bar0 + 40, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS,
+                   v_empty = v_full + 8 * NS;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) causal tiles first
+    const int q0 = q_tile * BM;
+    const int bh = blockIdx.y;
+    const int b = bh / p.Hq, h = bh % p.Hq;
+    const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
+
+    int kv_limit = p.Sk;                                   // keys any row of this batch may see
+    if (p.kv_lens) kv_limit = min(kv_limit, max(p.kv_lens[b], 0));
+    int kv_end = kv_limit;                                 // keys this query tile may see
+    if (p.causal) kv_end = min(kv_end, q0 + BM);
+    const int n_tiles = (kv_end + BN - 1) / BN;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        ptx::mbar_init(q_full, 1);
+        ptx::mbar_init(s_full, 1);
+        ptx::mbar_init(s_free, 128);
+        ptx::mbar_init(p_full, 128);
+        ptx::mbar_init(pv_done, 1);
+        for (int s = 0; s < NS; ++s) {
+            ptx::mbar_init(k_full + 8 * s, 1);
+            ptx::mbar_init(k_empty + 8 * s, 1);
+            ptx::mbar_init(v_full + 8 * s, 1);
+            ptx::mbar_init(v_empty + 8 * s, 1);
+        }
+        ptx::fence_mbar_init();
+        if (sbase & 1023u) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_ALIGN); }
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), Cfg::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const bool run = (*abort_flag == 0) && n_tiles > 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0 && run) {
+            ptx::prefetch_tmap(&tm_q);
+            ptx::prefetch_tmap(&tm_k);
+            ptx::prefetch_tmap(&tm_v);
+            ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+            for (int pn = 0; pn < Cfg::DP; ++pn)
+                ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::KV_BYTES);
+                for (int pn = 0; pn < Cfg::DP; ++pn)
+                    ptx::tma_load_3d(k_s + s * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_k,
+                                     k_full + 8 * s, pn * 64, j * BN, kvh);
+                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::KV_BYTES);
+                for (int pn = 0; pn < Cfg::DP; ++pn)
+                    ptx::tma_load_3d(v_s + s * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                     v_full + 8 * s, pn * 64, j * BN, kvh);
+            }
+            if (!ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && run) {
+            constexpr uint32_t idesc_qk = ptx::idesc_f16(BM, BN, false);
+            constexpr uint32_t idesc_pv = ptx::idesc_f16(BM, D, true);
+            const uint32_t t_s = tmem + Cfg::COL_S, t_o = tmem + Cfg::COL_O, t_p = tmem + Cfg::COL_P;
+            bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag)) return false;
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t a = q_s + (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+                    const uint32_t bb = k_s + s * Cfg::KV_BYTES + (kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32;
+                    ptx::mma_ss(t_s, ptx::smem_desc_sw128(a, 16, 1024),
+                                ptx::smem_desc_sw128(bb, 16, 1024), idesc_qk, kk > 0);
+                }
+                ptx::mma_commit(k_empty + 8 * s);
+                ptx::mma_commit(s_full);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = ptx::mbar_wait(s_free, (uint32_t)j & 1u, abort_flag);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                ok = ptx::mbar_wait(v_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                ok = ptx::mbar_wait(p_full, (uint32_t)j & 1u, abort_flag);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    // V stage: D/64 panels of [BN keys][64 cols]; 16 keys = 2 KB further down
+                    const uint32_t vb = v_s + s * Cfg::KV_BYTES + kk * (16 * 128);
+                    const uint64_t bdesc = ptx::smem_desc_sw128(vb, Cfg::KV_PANEL, 1024);
+                    const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+                    if constexpr (Cfg::P_TMEM) {
+                        ptx::mma_ts(t_o, t_p + kk * 8, bdesc, idesc_pv, acc);
+                    } else {
+                        const uint32_t pa = p_s + (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+                        ptx::mma_ss(t_o, ptx::smem_desc_sw128(pa, 16, 1024), bdesc, idesc_pv, acc);
+                    }
+                }
+                ptx::mma_commit(v_empty + 8 * s);
+                ptx::mma_commit(pv_done);
+            }
+            if (!ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_MMA); }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue
+        const int quarter = warp & 3;                    // tensor-memory lanes this warp may touch
+        const int r = quarter * 32 + lane;               // row inside the tile
+        const int row = q0 + r;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem + lane_base + Cfg::COL_S;
+        const uint32_t t_o = tmem + lane_base + Cfg::COL_O;
+        const uint32_t t_p = tmem + lane_base + Cfg::COL_P;
+        float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
+        float l = 0.f;
+        bool ok = run;
+        // waits are made warp-uniform so that the .sync.aligned tensor-memory
+        // instructions below are always executed by the whole warp
+        auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
+            return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+        };
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int kv0 = j * BN;
+            ok = wait_all(s_full, (uint32_t)j & 1u);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
+            // pass 1: row maximum of the visible scores
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld32(t_s + c * 32, v);
+                ptx::tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = kv0 + c * 32 + i;
+                        const bool vis = col < kv_limit && (!p.causal || col <= row);
+                        mx = fmaxf(mx, vis ? __uint_as_float(v[i]) : -INFINITY);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m_used, mx * p.scale_log2);
+            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+            // pass 2: p = 2^(s*scale - m), row sum in fp32, pack to fp16 pairs
+            uint32_t pk[BN / 2];
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld32(t_s + c * 32, v);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float e0 = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_next));
+                    float e1 = ptx::ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_next));
+                    if (need_mask) {
+                        const int col = kv0 + c * 32 + i;
+                        if (!(col < kv_limit && (!p.causal || col <= row))) e0 = 0.f;
+                        if (!(col + 1 < kv_limit && (!p.causal || col + 1 <= row))) e1 = 0.f;
+                    }
+                    sum += e0 + e1;
+                    pk[c * 16 + i / 2] = ptx::pack_half2(e0, e1);
+                }
+            }
+            // S has been read twice and is no longer needed: let QK^T of the next tile start
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(s_free);
+            l = l * alpha + sum;
+            m_used = m_next;
+            if (j > 0) {
+                // PV of the previous tile must be finished before P is overwritten or O rescaled
+                ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        ptx::tmem_ld32(t_o + c * 32, o);
+                        ptx::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st32(t_o + c * 32, o);
+                    }
+                    ptx::tmem_wait_st();
+                }
+            }
+            if constexpr (Cfg::P_TMEM) {
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t t[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) t[i] = pk[c * 32 + i];
+                    ptx::tmem_st32(t_p + c * 32, t);
+                }
+                ptx::tmem_wait_st();
+            } else {
+                // row r of P: BN/64 panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
+#pragma unroll
+                for (int ch = 0; ch < BN / 8; ++ch) {
+                    const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
+                                          (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
+                    ptx::st_shared_v4(addr, pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                }
+                ptx::fence_proxy_async_smem();
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(p_full);
+        }
+        if (run && ok) {
+            ok = wait_all(pv_done, (uint32_t)(n_tiles - 1) & 1u);
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
+                float *orow = p.out + ((size_t)bh * p.Sq + row) * D;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld32(t_o + c * 32, o);
+                    ptx::tmem_wait_ld();
+                    if (row < p.Sq) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 f;
+                            f.x = __uint_as_float(o[i]) * inv_l;
+                            f.y = __uint_as_float(o[i + 1]) * inv_l;
+                            f.z = __uint_as_float(o[i + 2]) * inv_l;
+                            f.w = __uint_as_float(o[i + 3]) * inv_l;
+                            *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
+                        }
+                    }
+                }
+            }
+        }
+        if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
+        if (!run && *abort_flag == 0 && row < p.Sq) {
+            // no visible key at all for this tile: the reference's 0/0
+            float *orow = p.out + ((size_t)bh * p.Sq + row) * D;
+            for (int i = 0; i < D; ++i) orow[i] = __int_as_float(0x7fc00000);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before the CTA's memory goes away
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace txb
