@@ -98,6 +98,13 @@ TX_API int tx_sdpa_mma_fp16_cuda(const void *Q_h, const void *K_h, const void *V
  *      reference it does not synchronise (stream order is enough). */
 TX_API int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size);
 
+/* ---- K/V head replication: reference csrc/tensor_ops.cpp:121-162 (repeat_interleave),
+ *      which round-trips through host memory.  Here it is one device gather:
+ *      out[i, j*repeats + r, k] = in[i, j, k] for i < outer, j < dim_size, k < inner.
+ *      elem_bytes is 2 or 4.  Does not synchronise. */
+TX_API int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t dim_size,
+                                     int64_t inner, int64_t repeats, int32_t elem_bytes);
+
 /* ---- general form (no reference counterpart: the reference has no fp16+mask,
  *      no implicit causal / key-length mask and no grouped K/V heads; its dense
  *      mask forms cannot exist at S = 8192).  Asynchronous on `stream`. */

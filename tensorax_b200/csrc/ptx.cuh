@@ -62,17 +62,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` is a shared-memory word any thread of the CTA sets
-// when it gives up; everybody else then stops waiting at once.  One try_wait
-// suspends for up to a hardware time limit (of the order of a microsecond to a
-// millisecond), so the cap below is seconds at most.
-constexpr uint32_t kWaitSpins = 1u << 22;
+// when it gives up; everybody else then stops waiting at once.  The bound is
+// wall-clock (the nanosecond global timer), not a spin count, because one
+// try_wait may itself suspend for a hardware-chosen time.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
 {
-    for (uint32_t i = 0; i < kWaitSpins; ++i) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && *abort_flag) return false;
+        if ((i & 127u) == 127u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
     }
-    return false;
 }
 
 // ---------------------------------------------------------------- fences

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -270,6 +271,19 @@ __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__r
     }
 }
 
+template <typename T>
+__global__ void repeat_interleave_kernel(const T *__restrict__ in, T *__restrict__ out, int64_t total,
+                                         int64_t dim_size, int64_t inner, int64_t repeats)
+{
+    for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total;
+         o += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t k = o % inner;
+        const int64_t jr = (o / inner) % (dim_size * repeats);
+        const int64_t i = o / (inner * dim_size * repeats);
+        out[o] = in[(i * dim_size + jr / repeats) * inner + k];
+    }
+}
+
 // ------------------------------------------------------------------ host-buffer form
 struct Workspace {
     void *ptr = nullptr;
@@ -426,6 +440,27 @@ int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size)
     const int64_t blocks = (size + threads * 4 - 1) / (threads * 4);
     if (blocks > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "cast_to_fp16: tensor too large");
     cast_f32_to_f16_kernel<<<(unsigned)blocks, threads>>>(in, static_cast<__half *>(out), size);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t dim_size,
+                              int64_t inner, int64_t repeats, int32_t elem_bytes)
+{
+    if (!in || !out || outer <= 0 || dim_size <= 0 || inner <= 0 || repeats <= 0)
+        return fail(TX_ERR_INVALID, "repeat_interleave: bad arguments");
+    if (elem_bytes != 2 && elem_bytes != 4) return fail(TX_ERR_INVALID, "repeat_interleave: element size must be 2 or 4");
+    if (int rc = ensure_device()) return rc;
+    const int64_t total = outer * dim_size * repeats * inner;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + threads - 1) / threads, 148 * 16);
+    if (elem_bytes == 2)
+        repeat_interleave_kernel<uint16_t><<<blocks, threads>>>(static_cast<const uint16_t *>(in),
+                                                               static_cast<uint16_t *>(out), total, dim_size, inner, repeats);
+    else
+        repeat_interleave_kernel<uint32_t><<<blocks, threads>>>(static_cast<const uint32_t *>(in),
+                                                               static_cast<uint32_t *>(out), total, dim_size, inner, repeats);
     g_launches++;
     TX_CUDA(cudaGetLastError());
     return TX_OK;

@@ -133,6 +133,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         ptx::fence_mbar_init();
         if (sbase & 1023u) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_ALIGN); }
+        // another CTA of this (or an earlier, unchecked) launch already gave up: do not start
+        if (*reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), Cfg::TMEM_COLS);
