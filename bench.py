@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Benchmark of the SDPA forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: BASELINE config 2 -- fp16 Q/K/V, fp32 accumulate, B=4 H=8 S=8192 d=64,
+non-causal, no mask, scale 1/sqrt(d); FLOPs per pass = 4*B*H*S^2*d = 549.76 G.
+Inputs are seeded synthetic N(0,1) cast to fp16 (the reference benchmarks on
+random tensors too, benchmarks/attn_sweep.py:91-93).
+
+A step is one forward pass over one such batch.  With N ranks (launched by
+torch.distributed.run, one process per GPU) every rank owns the 32
+(batch, head) units of its own B=4 slice of a global batch of 4*N: weak
+scaling, no data-path collective; torch.distributed is used only for the
+barrier and for the max over ranks of the device time.
+
+Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events on the
+launching stream, inputs resident in HBM, L2 flushed between steps); `e2e` is
+the same metric through the host-buffer C-ABI call, pinned-host -> device copies
+and the device -> host copy of the result inside the timed region.
+
+`--impl reference` times the reference's own CPU SDPA (oracle/_ref, or the C
+restatement if the reference library was not built) on all host cores, on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, H, S, D = 4, 8, 8192, 64
+FLOPS_PER_STEP = 4.0 * B * H * S * S * D                    # 549.76 GFLOP, per GPU
+ALG_BYTES_PER_STEP = B * H * S * D * (2 + 2 + 2 + 4)        # Q,K,V fp16 reads + O fp32 write
+METRIC = "fp16 SDPA fwd TFLOP/s per GPU at B4 H8 S8192 d64; % of B200 dense fp16 peak"
+PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070 Ti Laptop (sm_86)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists)
+NCU_DRAM_BYTES_PER_LAUNCH = None
+WORKLOAD = "config2: SDPA fwd fp16 (fp32 accumulate) B=4 H=8 S=8192 d=64 non-causal, no mask"
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            mp = json.load(f)
+        return float(mp["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------------------- CPU legs
+def cpu_sdpa_sample(rows_per_slice: int, threads: int):
+    """Times the CPU SDPA on `threads` independent (b,h) slices at once, each
+    `rows_per_slice` query rows against all S keys of config 2.  Returns
+    (seconds, flops, kind)."""
+    import oracle
+    if oracle.have_reference():
+        fn, kind = oracle.ref_sdpa_cpu, "reference"
+    else:
+        fn, kind = oracle.sdpa_f32, "port"
+    rng = np.random.Generator(np.random.PCG64(0))
+    slices = []
+    for _ in range(threads):
+        q = rng.standard_normal((1, 1, rows_per_slice, D), dtype=np.float32).astype(np.float16).astype(np.float32)
+        k = rng.standard_normal((1, 1, S, D), dtype=np.float32).astype(np.float16).astype(np.float32)
+        v = rng.standard_normal((1, 1, S, D), dtype=np.float32).astype(np.float16).astype(np.float32)
+        slices.append((q, k, v))
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(lambda a: fn(*a), slices))
+    dt = time.perf_counter() - t0
+    return dt, 4.0 * threads * rows_per_slice * S * D, kind
+
+
+def host_threads():
+    try:
+        return max(len(os.sched_getaffinity(0)), 1)
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    threads = host_threads()
+    rows = 1024          # per slice and step: threads * 4*1024*8192*64 = threads * 2.15 GFLOP
+    for _ in range(args.warmup):
+        cpu_sdpa_sample(min(rows, 128), threads)
+    total_t, total_f, kind = 0.0, 0.0, "port"
+    for _ in range(args.steps):
+        dt, fl, kind = cpu_sdpa_sample(rows, threads)
+        total_t += dt
+        total_f += fl
+    tflops = total_f / total_t / 1e12
+    sample = (f"each step = {threads} concurrent (b,h) slices x {rows} query rows x all {S} keys of config 2 "
+              f"({threads * rows / (B * H * S):.4f} of one pass)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * (FLOPS_PER_STEP / (tflops * 1e12)),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "device": "host CPU"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "ms_per_step is the time one full pass would take at the sampled rate",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.tmp.read().splitlines():
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        if sm:
+            busy = sorted(sm)[len(sm) // 2:]            # upper half ~ samples taken under load
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args, rank, world, local_rank):
+    import torch
+    from tensorax_b200 import _lib
+
+    lib = _lib.load()
+    if not lib.tx_cuda_is_available():
+        raise SystemExit("bench.py: no CUDA device; the SDPA path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    _lib.check(lib.tx_cuda_set_device(local_rank))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)     # each rank: its own B=4 slice
+    n = B * H * S * D
+    host = [torch.randn(n, generator=gen, dtype=torch.float32).to(torch.float16).pin_memory() for _ in range(3)]
+    host_out = torch.empty(n, dtype=torch.float32).pin_memory()
+    q, k, v = (h.to(dev, non_blocking=True) for h in host)
+    out = torch.empty(n, dtype=torch.float32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)      # > 126 MB L2
+    stream = torch.cuda.current_stream(dev)
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+
+    def desc_for(qp, kp, vp, op):
+        return _lib.SdpaDesc(q=qp, k=kp, v=vp, mask=None, kv_lens=None, out=op, batch=B, q_heads=H, kv_heads=H,
+                             seq_q=S, seq_k=S, d_k=D, d_v=D, dtype=_lib.TX_DTYPE_F16, causal=0, flags=args.flags,
+                             stream=sptr)
+
+    dev_desc = desc_for(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr())
+    host_desc = desc_for(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host_out.data_ptr())
+    assert lib.tx_sdpa_uses_tensor_cores(ctypes.byref(dev_desc)) == 1, "config 2 must run on the tcgen05 kernel"
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- device-resident timing
+    for _ in range(max(args.warmup, 3)):
+        _lib.check(lib.tx_sdpa_forward(ctypes.byref(dev_desc)))
+    _lib.check(lib.tx_sdpa_finish(sptr))
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = lib.tx_kernel_launch_count()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)                                   # evict the previous step's lines from L2
+        starts[i].record(stream)
+        _lib.check(lib.tx_sdpa_forward(ctypes.byref(dev_desc)))
+        ends[i].record(stream)
+    _lib.check(lib.tx_sdpa_finish(sptr))
+    barrier()
+    launches = lib.tx_kernel_launch_count() - launches0
+    per_step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    ms = max_over_ranks(sum(per_step_ms) / len(per_step_ms))
+
+    # ---------------- end-to-end through the host-buffer entry point
+    for _ in range(2):
+        _lib.check(lib.tx_sdpa_forward_host(ctypes.byref(host_desc)))
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record(stream)
+    for _ in range(args.steps):
+        _lib.check(lib.tx_sdpa_forward_host(ctypes.byref(host_desc)))
+    e_end.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e_start.elapsed_time(e_end) / args.steps)
+    clocks = sampler.stop() if sampler else None
+    checksum = float(host_out[:: max(n // 4096, 1)].double().sum())
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak()
+    per_gpu = FLOPS_PER_STEP / (ms * 1e-3) / 1e12
+    kernel_ms = sum(per_step_ms) / len(per_step_ms)           # rank 0's own launches
+    achieved = FLOPS_PER_STEP / (kernel_ms * 1e-3) / 1e12
+    threads = host_threads()
+    cpu_dt, cpu_fl, cpu_kind = cpu_sdpa_sample(2048, threads)
+    line = {
+        "metric": METRIC, "value": per_gpu * world, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": per_gpu / PUBLISHED_TFLOPS,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": B * world, "heads": H, "seq_len": S, "head_dim": D,
+                   "parallelism": f"{world} rank(s) x 32 (batch,head) units each, no collective",
+                   "l2": "flushed between steps (256 MB write); inputs+output 160 MiB > 126 MB L2",
+                   "p_operand": "tensor memory" if args.flags & 2 else "shared memory"},
+        "per_gpu_tflops": per_gpu, "pct_of_peak": 100.0 * per_gpu / peak,
+        "vs_baseline_note": "published number is the reference kernel on an RTX 3070 Ti Laptop (README.md:80-82)",
+        "e2e": {"value": world * FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": e2e_ms, "h2d_bytes_per_step": 3 * n * 2, "d2h_bytes_per_step": n * 4,
+                "api": "tx_sdpa_forward_host (pinned host buffers)", "checksum": checksum},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_src,
+                     "kernel": "sdpa_tc_kernel<D=64,BN=128>", "flops_per_launch": FLOPS_PER_STEP,
+                     "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP,
+                     "hbm_gbs_algorithmic": ALG_BYTES_PER_STEP / (kernel_ms * 1e-3) / 1e9},
+        "cpu_baseline": {"value": cpu_fl / cpu_dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": cpu_kind,
+                         "sample": f"{threads} concurrent (b,h) slices x 2048 query rows x all {S} keys "
+                                   f"({threads * 2048 / (B * H * S):.4f} of one pass), {cpu_dt:.1f} s"},
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--flags", type=int, default=int(os.environ.get("TX_BENCH_FLAGS", "0")),
+                    help="TX_SDPA_* flags passed to the kernel selection (2 = P in tensor memory)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # started by hand without a launcher: start one rank per GPU the documented way
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

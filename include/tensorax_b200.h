@@ -54,6 +54,10 @@ TX_API int tx_version(void);
 /* ---- device memory helpers: reference csrc/cuda/tensor_cuda.cu:7-29
  *      (cuda_is_available, cuda_malloc, cuda_free, cuda_memcpy_h2d, cuda_memcpy_d2h) */
 TX_API int tx_cuda_is_available(void);
+/* one process drives one GPU: select it before anything else (no reference counterpart;
+ * the reference never leaves device 0) */
+TX_API int tx_cuda_device_count(void);
+TX_API int tx_cuda_set_device(int device);
 TX_API void *tx_cuda_malloc(size_t bytes);            /* NULL on failure */
 TX_API int tx_cuda_free(void *ptr);
 TX_API int tx_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes);

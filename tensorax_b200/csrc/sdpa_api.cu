@@ -181,12 +181,8 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
     p.Sk = (int)d->seq_k;
     p.causal = d->causal ? 1 : 0;
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
-    static bool attr_set = false;   // per template instantiation
-    if (!attr_set) {
-        TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)Cfg::SMEM_BYTES));
-        attr_set = true;
-    }
+    TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg::SMEM_BYTES));
     dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads));
     txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
     g_launches++;
@@ -326,6 +322,22 @@ int tx_cuda_is_available(void)
         return 0;
     }
     return n > 0 ? 1 : 0;
+}
+
+int tx_cuda_device_count(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int tx_cuda_set_device(int device)
+{
+    TX_CUDA(cudaSetDevice(device));
+    return TX_OK;
 }
 
 void *tx_cuda_malloc(size_t bytes)

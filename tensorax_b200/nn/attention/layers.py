@@ -1,0 +1,113 @@
+"""Attention layers with the reference's constructor arguments, ``forward``
+signatures and ``repr`` strings (tensorax/nn/attention/layers.py:8-135)."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from ... import functional as F
+from ...tensor import Tensor
+
+
+class ScaledDotProductAttention:
+    """Pass-through to ``F.scaled_dot_product_attention`` (layers.py:8-17)."""
+
+    def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        return F.scaled_dot_product_attention(query, key, value, mask)
+
+    def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        return self.forward(query, key, value, mask)
+
+    def __repr__(self) -> str:
+        return "ScaledDotProductAttention()"
+
+
+class GroupedQueryAttention:
+    """Grouped-query attention (layers.py:19-50).
+
+    ``forward`` keeps the reference's behaviour to the letter: K and V are
+    replicated ``num_heads // num_kv_heads`` times along dim 2 and the result is
+    handed to SDPA unchanged, so dim 1 is what SDPA treats as the head axis.
+    For the usual [batch, heads, seq, dim] layout with fewer K/V heads, use
+    ``forward_bhsd``: no copy is made, query head h reads K/V head
+    h // (num_heads // num_kv_heads) inside the kernel.
+    """
+
+    def __init__(self, num_heads: int, num_kv_heads: int):
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        assert num_heads % num_kv_heads == 0, "num_heads must be divisible by num_kv_heads"
+        self.num_queries_per_kv = num_heads // num_kv_heads
+
+    def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        if self.num_queries_per_kv > 1:
+            key = key.repeat_interleave(self.num_queries_per_kv, dim=2)
+            value = value.repeat_interleave(self.num_queries_per_kv, dim=2)
+        return F.scaled_dot_product_attention(query, key, value, mask)
+
+    def forward_bhsd(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None,
+                     causal: bool = False, kv_lens=None) -> Tensor:
+        """query [B, num_heads, S, d]; key/value [B, num_kv_heads, S, d]."""
+        if query.shape[1] != self.num_heads or key.shape[1] != self.num_kv_heads:
+            raise ValueError("forward_bhsd: head counts do not match the layer")
+        return F.scaled_dot_product_attention_ex(query, key, value, mask, causal=causal, kv_lens=kv_lens)
+
+    def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        return self.forward(query, key, value, mask)
+
+    def __repr__(self) -> str:
+        return f"GroupedQueryAttention(num_heads={self.num_heads}, num_kv_heads={self.num_kv_heads})"
+
+
+class MultiHeadAttention:
+    """Multi-head attention (layers.py:53-135): same constructor, parameters,
+    initialisation scale and ``repr``.
+
+    The reference's ``forward`` cannot run (it calls the unbound
+    ``_C.transpose_dims``, tensorax/tensor.py:976).  The attention it would issue
+    is the SDPA call on [batch, num_heads, seq, head_dim] (layers.py:122);
+    ``attend`` runs exactly that call.  The four projections are GEMMs outside
+    this package's scope, so ``forward`` raises until they are built.
+    """
+
+    def __init__(self, embed_dim: int, num_heads: int, bias: bool = True, dropout: float = 0.0):
+        if embed_dim % num_heads != 0:
+            raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads})")
+        self.embed_dim = embed_dim
+        self.num_heads = num_heads
+        self.head_dim = embed_dim // num_heads
+        self.dropout = dropout
+        self._parameters = {}
+        std = math.sqrt(2.0 / (embed_dim + embed_dim))
+        rng = np.random.default_rng()
+        for name in ("q_weight", "k_weight", "v_weight", "out_weight"):
+            w = (rng.standard_normal((embed_dim, embed_dim)) * std).astype(np.float32)
+            self._parameters[name] = Tensor(w, requires_grad=True)
+        for name in ("q_bias", "k_bias", "v_bias", "out_bias"):
+            self._parameters[name] = Tensor.zeros((embed_dim,), requires_grad=True) if bias else None
+
+    def parameters(self):
+        return [p for p in self._parameters.values() if p is not None]
+
+    def attend(self, q: Tensor, k: Tensor, v: Tensor, mask: Tensor = None, causal: bool = False,
+               kv_lens=None) -> Tensor:
+        """The SDPA step of forward (layers.py:122) on already projected and
+        head-split tensors [batch, num_heads, seq, head_dim]."""
+        if q.shape[1] != self.num_heads or q.shape[3] != self.head_dim:
+            raise ValueError("attend: expected [batch, num_heads, seq, head_dim]")
+        if causal or kv_lens is not None:
+            return F.scaled_dot_product_attention_ex(q, k, v, mask, causal=causal, kv_lens=kv_lens)
+        return F.scaled_dot_product_attention(q, k, v, mask)
+
+    def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        raise NotImplementedError(
+            "MultiHeadAttention.forward needs the Q/K/V/output projection GEMMs, which are outside "
+            "the SDPA forward path this package implements; project and split heads, then call attend()")
+
+    def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+        return self.forward(query, key, value, mask)
+
+    def __repr__(self) -> str:
+        return (f"MultiHeadAttention(embed_dim={self.embed_dim}, num_heads={self.num_heads}, "
+                f"head_dim={self.head_dim}, dropout={self.dropout})")
