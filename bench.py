@@ -165,8 +165,7 @@ class ClockSampler:
         self.tmp.close()
         os.unlink(self.tmp.name)
         if sm:
-            busy = sorted(sm)[len(sm) // 2:]            # upper half ~ samples taken under load
-            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
 
 
