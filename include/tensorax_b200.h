@@ -142,6 +142,41 @@ TX_API int64_t tx_kernel_launch_count(void);
  *      the library and reused between calls. */
 TX_API int tx_sdpa_forward_host(const tx_sdpa_desc *desc);
 
+/* ---- allocation-free form (no counterpart in the reference).
+ *
+ * For callers that must not, or cannot, allocate device memory while they run
+ * attention: a host program whose device memory is handed out once, up front, by
+ * its own arena or memory planner and that forbids libraries from calling
+ * cudaMalloc behind its back; a serving loop that cannot afford the device-wide
+ * synchronisation an allocation implies; a process already at its memory limit.
+ * Every other entry point of this library may allocate (a status word per
+ * device on first use, staging buffers in the _host form).
+ *
+ * This one allocates nothing, ever.  The tensor-core kernel's scratch -- the
+ * status word its bounded waits report through and the device copy of the
+ * per-batch key lengths -- lives in a fixed array that is part of the loaded
+ * library image on every GPU (TX_STATIC_SCRATCH_BYTES, held until the process
+ * exits).  The caller passes inputs and outputs as usual; `kv_lens_host` is a
+ * HOST array of `batch` lengths, or NULL.
+ *
+ * Limits: fp16 inputs, d_k == d_v in {64, 128}, 16-byte aligned pointers (the
+ * shapes the tensor-core kernel takes -- others are refused with
+ * TX_ERR_UNSUPPORTED, never routed elsewhere), and batch <=
+ * TX_STATIC_SCRATCH_MAX_BATCH when key lengths are given (TX_ERR_INVALID beyond).
+ *
+ * The first call on a device looks up the array's device address once; make
+ * that first call before any stream capture begins.  All calls on one GPU share
+ * the array: the entry point clears the status word and overwrites the lengths
+ * itself, but two calls whose kernels may overlap on the GPU (different
+ * streams, or different host threads) race on it -- serialise them.
+ * Returns after `out` is complete, like the reference launchers. */
+#define TX_STATIC_SCRATCH_MAX_BATCH 4096
+#define TX_STATIC_SCRATCH_BYTES (256 + 4 * TX_STATIC_SCRATCH_MAX_BATCH)
+TX_API int tx_sdpa_fp16_static_scratch(const void *Q_h, const void *K_h, const void *V_h, float *out,
+                                       int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                       int64_t seq_q, int64_t seq_k, int64_t d, int32_t causal,
+                                       const int32_t *kv_lens_host, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_optimized_flash_cuda", "tx_sdpa_mma_cuda", "tx_sdpa_mma_fp16_cuda",
     "tx_cast_f32_to_f16_cuda", "tx_repeat_interleave_cuda",
     "tx_sdpa_forward", "tx_sdpa_finish", "tx_sdpa_uses_tensor_cores",
-    "tx_kernel_launch_count", "tx_sdpa_forward_host",
+    "tx_kernel_launch_count", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
 )
 
 
@@ -87,6 +87,7 @@ def load():
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_uses_tensor_cores.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_finish.argtypes = [c_void_p]
+    lib.tx_sdpa_fp16_static_scratch.argtypes = [c_void_p] * 4 + [c_int64] * 6 + [c_int32, c_void_p, c_void_p]
     lib.tx_kernel_launch_count.restype = c_int64
     _lib = lib
     return lib

@@ -307,6 +307,32 @@ int workspace(size_t bytes, void **out)
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// ------------------------------------------------------------------ allocation-free form
+// Scratch of tx_sdpa_fp16_static_scratch: [0,256) status word (+ padding), then up to
+// TX_STATIC_SCRATCH_MAX_BATCH key lengths.  It is part of the module image on every GPU that
+// loads the library.  In host code the name below is only a handle for
+// cudaGetSymbolAddress; kernels are given the address that call returns.
+static __device__ __align__(256) unsigned char g_static_scratch[TX_STATIC_SCRATCH_BYTES];
+unsigned char *g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of the array on the current device, looked up once per device.
+int static_scratch(unsigned char **out)
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TX_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_scratch_addr[dev]) {
+        unsigned char *ptr = nullptr;
+        TX_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch));
+        if (!ptr) return fail(TX_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return TX_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -520,6 +546,46 @@ int tx_sdpa_forward_host(const tx_sdpa_desc *h)
     if (int rc = forward(&d)) return rc;
     TX_CUDA(cudaMemcpyAsync(h->out, w + oo, no, cudaMemcpyDeviceToHost, st));
     return finish(st);
+}
+
+int tx_sdpa_fp16_static_scratch(const void *Q_h, const void *K_h, const void *V_h, float *out,
+                                int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t seq_q,
+                                int64_t seq_k, int64_t d, int32_t causal, const int32_t *kv_lens_host,
+                                void *stream)
+{
+    tx_sdpa_desc desc;
+    std::memset(&desc, 0, sizeof desc);
+    desc.q = Q_h; desc.k = K_h; desc.v = V_h; desc.out = out;
+    desc.batch = batch; desc.q_heads = q_heads; desc.kv_heads = kv_heads;
+    desc.seq_q = seq_q; desc.seq_k = seq_k; desc.d_k = d; desc.d_v = d;
+    desc.dtype = TX_DTYPE_F16;
+    desc.causal = causal;
+    desc.stream = stream;
+    if (int rc = validate(&desc)) return rc;
+    if (kv_lens_host && batch > TX_STATIC_SCRATCH_MAX_BATCH)
+        return fail(TX_ERR_INVALID, "static-scratch SDPA: batch %lld exceeds the %d key lengths the fixed scratch holds",
+                    (long long)batch, TX_STATIC_SCRATCH_MAX_BATCH);
+    if (!tc_eligible(&desc))
+        return fail(TX_ERR_UNSUPPORTED,
+                    "static-scratch SDPA: only the tensor-core shapes are taken (fp16, d_k == d_v in {64,128}, "
+                    "16-byte aligned pointers, batch*heads <= 65535)");
+    if (int rc = ensure_device()) return rc;
+    unsigned char *scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int *status = reinterpret_cast<int *>(scratch);
+    TX_CUDA(cudaMemsetAsync(status, 0, 256, st));            // the array keeps the last call's contents
+    if (kv_lens_host) {
+        TX_CUDA(cudaMemcpyAsync(scratch + 256, kv_lens_host, (size_t)batch * 4, cudaMemcpyHostToDevice, st));
+        desc.kv_lens = reinterpret_cast<const int32_t *>(scratch + 256);
+    }
+    if (int rc = launch_tc(&desc, st, status)) return rc;
+    int code = 0;
+    TX_CUDA(cudaMemcpyAsync(&code, status, sizeof code, cudaMemcpyDeviceToHost, st));
+    TX_CUDA(cudaStreamSynchronize(st));
+    if (code != 0)
+        return fail(TX_ERR_KERNEL, "SDPA kernel gave up on a bounded wait (stage code %d); output is not valid", code);
+    return TX_OK;
 }
 
 }  // extern "C"
