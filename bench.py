@@ -272,7 +272,7 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": WORKLOAD, "global_batch": B * world, "heads": H, "seq_len": S, "head_dim": D,
                    "parallelism": f"{world} rank(s) x 32 (batch,head) units each, no collective",
                    "l2": "flushed between steps (256 MB write); inputs+output 160 MiB > 126 MB L2",
-                   "p_operand": "tensor memory" if args.flags & 2 else "shared memory"},
+                   "p_operand": "shared memory" if args.flags & 2 else "tensor memory"},
         "per_gpu_tflops": per_gpu, "pct_of_peak": 100.0 * per_gpu / peak,
         "vs_baseline_note": "published number is the reference kernel on an RTX 3070 Ti Laptop (README.md:80-82)",
         "e2e": {"value": world * FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -301,7 +301,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--flags", type=int, default=int(os.environ.get("TX_BENCH_FLAGS", "0")),
-                    help="TX_SDPA_* flags passed to the kernel selection (2 = P in tensor memory)")
+                    help="TX_SDPA_* flags passed to the kernel selection (2 = stage P in shared memory)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

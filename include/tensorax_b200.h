@@ -44,7 +44,8 @@ enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
 /* flags of tx_sdpa_desc */
 enum {
     TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
-    TX_SDPA_P_IN_TMEM = 2    /* tensor-core kernel: keep P in tensor memory instead of shared memory */
+    TX_SDPA_P_IN_SMEM = 2    /* tensor-core kernel: stage P in shared memory instead of tensor memory
+                                (ignored for d = 512, where shared memory has no room for it) */
 };
 
 /* Message of the last failure on the calling thread ("" if none). */
@@ -159,7 +160,7 @@ TX_API int tx_sdpa_forward_host(const tx_sdpa_desc *desc);
  * exits).  The caller passes inputs and outputs as usual; `kv_lens_host` is a
  * HOST array of `batch` lengths, or NULL.
  *
- * Limits: fp16 inputs, d_k == d_v in {64, 128}, 16-byte aligned pointers (the
+ * Limits: fp16 inputs, d_k == d_v in {64, 128, 256, 512}, 16-byte aligned pointers (the
  * shapes the tensor-core kernel takes -- others are refused with
  * TX_ERR_UNSUPPORTED, never routed elsewhere), and batch <=
  * TX_STATIC_SCRATCH_MAX_BATCH when key lengths are given (TX_ERR_INVALID beyond).

@@ -17,7 +17,7 @@ TX_OK = 0
 TX_DTYPE_F32 = 0
 TX_DTYPE_F16 = 1
 TX_SDPA_FORCE_SIMT = 1
-TX_SDPA_P_IN_TMEM = 2
+TX_SDPA_P_IN_SMEM = 2
 
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (

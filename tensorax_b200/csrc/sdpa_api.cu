@@ -134,7 +134,8 @@ bool tc_eligible(const tx_sdpa_desc *d)
 {
     if (d->flags & TX_SDPA_FORCE_SIMT) return false;
     if (d->dtype != TX_DTYPE_F16 || d->mask) return false;
-    if (d->d_k != d->d_v || (d->d_k != 64 && d->d_k != 128)) return false;
+    if (d->d_k != d->d_v) return false;
+    if (d->d_k != 64 && d->d_k != 128 && d->d_k != 256 && d->d_k != 512) return false;
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!al(d->q) || !al(d->k) || !al(d->v) || !al(d->out)) return false;
     if (d->batch * d->q_heads > 65535) return false;   // grid.y
@@ -179,26 +180,39 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
     p.Hkv = (int)d->kv_heads;
     p.Sq = (int)d->seq_q;
     p.Sk = (int)d->seq_k;
+    p.dv_total = (int)d->d_v;
     p.causal = d->causal ? 1 : 0;
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
     TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::SMEM_BYTES));
-    dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads));
+    dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads),
+              (unsigned)(d->d_v / Cfg::DV));
     txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
     g_launches++;
     TX_CUDA(cudaGetLastError());
     return TX_OK;
 }
 
+// Tile shapes per head dim (template arguments: DK, DV per CTA, keys per tile, ring depth, P in TMEM).
+//   d= 64: 128 keys/tile, two CTAs per SM      d=128: 64 keys/tile, two CTAs per SM
+//   d=256: 64 keys/tile, one CTA per SM        d=512: 32 keys/tile, two CTAs split the value columns
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
-    const bool ptm = (d->flags & TX_SDPA_P_IN_TMEM) != 0;
-    if (d->d_k == 64) {
-        if (ptm) return launch_tc_t<txb::TcCfg<64, 128, 2, true>>(d, st, status);
-        return launch_tc_t<txb::TcCfg<64, 128, 2, false>>(d, st, status);
+    const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
+    switch (d->d_k) {
+    case 64:
+        if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
+        return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
+    case 128:
+        if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
+        return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
+    case 256:
+        if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
+        return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true>>(d, st, status);
+    case 512:
+        return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true>>(d, st, status);
     }
-    if (ptm) return launch_tc_t<txb::TcCfg<128, 64, 2, true>>(d, st, status);
-    return launch_tc_t<txb::TcCfg<128, 64, 2, false>>(d, st, status);
+    return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
 }
 
 int forward(const tx_sdpa_desc *d)
@@ -567,7 +581,7 @@ int tx_sdpa_fp16_static_scratch(const void *Q_h, const void *K_h, const void *V_
                     (long long)batch, TX_STATIC_SCRATCH_MAX_BATCH);
     if (!tc_eligible(&desc))
         return fail(TX_ERR_UNSUPPORTED,
-                    "static-scratch SDPA: only the tensor-core shapes are taken (fp16, d_k == d_v in {64,128}, "
+                    "static-scratch SDPA: only the tensor-core shapes are taken (fp16, d_k == d_v in {64,128,256,512}, "
                     "16-byte aligned pointers, batch*heads <= 65535)");
     if (int rc = ensure_device()) return rc;
     unsigned char *scratch = nullptr;

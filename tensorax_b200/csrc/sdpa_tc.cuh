@@ -9,19 +9,25 @@
 // and causal / key-length masks and grouped K/V heads are applied in-kernel,
 // which the reference path cannot do at all.
 //
-// One CTA = one 128-row query tile of one (batch, query head).  Six warps:
+// One CTA = one 128-row query tile of one (batch, query head) and one slice of DV
+// value columns (the slice is the whole head except for d = 512, where two CTAs
+// each recompute S and own 256 output columns, as the reference's D_V_PASSES does
+// in sequence, attn.cu:1239-1241).  Six warps:
 //   warp 0      TMA producer (one lane): Q once, then K/V tiles through an
 //               NS-deep ring of shared-memory stages, 128-byte swizzled
 //   warp 1      owns tensor memory (alloc/dealloc); one lane issues every MMA:
 //               S = Q K^T (M=128, N=BN, K=16 per instruction) and
-//               O += P V  (M=128, N=D,  K=16 per instruction, V read MN-major)
+//               O += P V  (M=128, N=DV, K=16 per instruction, V read MN-major)
 //   warps 2-5   softmax: thread t owns query row 32*(warp%4)+lane, the tensor
-//               memory lane it is allowed to read.  Two passes over S in
-//               32-column chunks (row max, then exp2 + fp16 pack), O rescaled in
-//               tensor memory only when the running max grew by more than 2^8,
-//               masks applied in registers, epilogue O/l -> global fp32.
-// Two such CTAs fit one SM (shared memory <= 113 KB, 256 tensor-memory columns,
-// <= 168 registers), so one CTA's softmax overlaps the other's MMAs.
+//               memory lane it is allowed to read.  The whole S row is pulled into
+//               registers with one wait, S is handed back to the MMA warp at once,
+//               then: masks in registers, row max, exp2, fp16 pack, P written to
+//               tensor memory (or swizzled shared memory).  O is rescaled in tensor
+//               memory only when the running max grew by more than 2^8; the epilogue
+//               writes O/l as fp32.
+// For d <= 128 two such CTAs fit one SM (shared memory <= 113 KB, 256
+// tensor-memory columns, <= 168 registers), so one CTA's softmax overlaps the
+// other's MMAs.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in
 // `status` and the whole CTA drains and frees its tensor memory.
@@ -31,12 +37,13 @@
 namespace txb {
 
 struct TcParams {
-    float *out;               // [B,Hq,Sq,D] fp32
+    float *out;               // [B,Hq,Sq,dv_total] fp32
     const int32_t *kv_lens;   // optional [B]
     int *status;              // device word: 0 = ok, else first failing wait's code
     int Hq, Hkv, Sq, Sk;
+    int dv_total;             // row length of `out` (= DV * gridDim.z)
     int causal;
-    float scale_log2;         // (1/sqrt(d)) * log2(e)
+    float scale_log2;         // (1/sqrt(d_k)) * log2(e)
 };
 
 enum TcStatus : int {
@@ -47,40 +54,45 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int D_, int BN_, int NS_, bool P_TMEM_>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_>
 struct TcCfg {
-    static constexpr int D = D_;          // head dim (d_k == d_v)
+    static constexpr int DK = DK_;        // head dim of Q and K
+    static constexpr int DV = DV_;        // value columns this CTA owns
     static constexpr int BN = BN_;        // keys per tile
     static constexpr int NS = NS_;        // K/V ring depth
     static constexpr bool P_TMEM = P_TMEM_;
     static constexpr int BM = 128;        // query rows per CTA
     static constexpr int THREADS = 192;
-    static constexpr int DP = D / 64;     // 64-column (128-byte) panels per row of Q/K/V
-    static constexpr int NP = BN / 64;    // panels per row of P
-    static constexpr uint32_t Q_BYTES = BM * D * 2;
-    static constexpr uint32_t KV_BYTES = BN * D * 2;       // one K or V stage
+    static constexpr int KP = DK / 64;    // 64-column (128-byte) panels per row of Q / K
+    static constexpr int VP = DV / 64;    // panels per row of this CTA's V slice
+    static constexpr uint32_t Q_BYTES = BM * DK * 2;
+    static constexpr uint32_t K_BYTES = BN * DK * 2;       // one K stage
+    static constexpr uint32_t V_BYTES = BN * DV * 2;       // one V stage
     static constexpr uint32_t KV_PANEL = BN * 128;         // one 64-column panel of a stage
     static constexpr uint32_t P_BYTES = P_TMEM ? 0 : BM * BN * 2;
     static constexpr uint32_t OFF_Q = 0;
     static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
-    static constexpr uint32_t OFF_V = OFF_K + NS * KV_BYTES;
-    static constexpr uint32_t OFF_P = OFF_V + NS * KV_BYTES;
+    static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
+    static constexpr uint32_t OFF_P = OFF_V + NS * V_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
     // barriers: q_full, s_full, s_free, p_full, pv_done, then k_full/k_empty/v_full/v_empty[NS]
     static constexpr int N_BARS = 5 + 4 * NS;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
-    // tensor memory columns: S fp32 [BN] | O fp32 [D] | P fp16 pairs [BN/2] (only if P_TMEM)
+    // tensor memory columns: S fp32 [BN] | O fp32 [DV] | P fp16 pairs [BN/2] (only if P_TMEM)
     static constexpr uint32_t COL_S = 0;
     static constexpr uint32_t COL_O = BN;
-    static constexpr uint32_t COL_P = BN + D;
-    static constexpr uint32_t COLS_USED = BN + D + (P_TMEM ? BN / 2 : 0);
+    static constexpr uint32_t COL_P = BN + DV;
+    static constexpr uint32_t COLS_USED = BN + DV + (P_TMEM ? BN / 2 : 0);
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 32 ? 32 : COLS_USED <= 64 ? 64
                                         : COLS_USED <= 128 ? 128 : COLS_USED <= 256 ? 256 : 512;
-    static_assert(D % 64 == 0 && BN % 64 == 0, "panels are 64 columns wide");
+    static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
+    static_assert(DK % 64 == 0 && DV % 64 == 0, "panels are 64 columns wide");
+    static_assert(BN % 32 == 0 && (P_TMEM || BN % 64 == 0), "P in shared memory needs 64-column panels");
     static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
-    static_assert(BN <= 256 && D <= 256, "one MMA instruction covers N <= 256");
+    static_assert(BN <= 256 && DV <= 256, "one MMA instruction covers N <= 256");
+    static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA may have");
 };
 
 // Running-max growth (in log2 units) tolerated before O and l are rescaled.
@@ -88,11 +100,11 @@ struct TcCfg {
 constexpr float kLazyRescaleLog2 = 8.0f;
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, (Cfg::SMEM_BYTES <= 115712 && Cfg::TMEM_COLS <= 256) ? 2 : 1)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const TcParams p)
 {
-    constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
+    constexpr int DK = Cfg::DK, DV = Cfg::DV, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t q_s = sbase + Cfg::OFF_Q, k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V;
@@ -109,6 +121,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) causal tiles first
     const int q0 = q_tile * BM;
     const int bh = blockIdx.y;
+    const int dv0 = (int)blockIdx.z * DV;                      // first value column of this CTA
     const int b = bh / p.Hq, h = bh % p.Hq;
     const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
 
@@ -153,7 +166,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ptx::prefetch_tmap(&tm_k);
             ptx::prefetch_tmap(&tm_v);
             ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-            for (int pn = 0; pn < Cfg::DP; ++pn)
+            for (int pn = 0; pn < Cfg::KP; ++pn)
                 ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
@@ -161,16 +174,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
                 ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
-                ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::KV_BYTES);
-                for (int pn = 0; pn < Cfg::DP; ++pn)
-                    ptx::tma_load_3d(k_s + s * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_k,
+                ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+                for (int pn = 0; pn < Cfg::KP; ++pn)
+                    ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
                                      k_full + 8 * s, pn * 64, j * BN, kvh);
                 ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
-                ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::KV_BYTES);
-                for (int pn = 0; pn < Cfg::DP; ++pn)
-                    ptx::tma_load_3d(v_s + s * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_v,
-                                     v_full + 8 * s, pn * 64, j * BN, kvh);
+                ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
+                for (int pn = 0; pn < Cfg::VP; ++pn)
+                    ptx::tma_load_3d(v_s + s * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                     v_full + 8 * s, dv0 + pn * 64, j * BN, kvh);
             }
             if (!ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
         }
@@ -178,7 +191,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && run) {
             constexpr uint32_t idesc_qk = ptx::idesc_f16(BM, BN, false);
-            constexpr uint32_t idesc_pv = ptx::idesc_f16(BM, D, true);
+            constexpr uint32_t idesc_pv = ptx::idesc_f16(BM, DV, true);
             const uint32_t t_s = tmem + Cfg::COL_S, t_o = tmem + Cfg::COL_O, t_p = tmem + Cfg::COL_P;
             bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
             auto issue_qk = [&](int j) -> bool {
@@ -187,9 +200,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag)) return false;
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
+                for (int kk = 0; kk < DK / 16; ++kk) {
                     const uint32_t a = q_s + (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-                    const uint32_t bb = k_s + s * Cfg::KV_BYTES + (kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32;
+                    const uint32_t bb = k_s + s * Cfg::K_BYTES + (kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32;
                     ptx::mma_ss(t_s, ptx::smem_desc_sw128(a, 16, 1024),
                                 ptx::smem_desc_sw128(bb, 16, 1024), idesc_qk, kk > 0);
                 }
@@ -215,8 +228,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 ptx::tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    // V stage: D/64 panels of [BN keys][64 cols]; 16 keys = 2 KB further down
-                    const uint32_t vb = v_s + s * Cfg::KV_BYTES + kk * (16 * 128);
+                    // V stage: DV/64 panels of [BN keys][64 cols]; 16 keys = 2 KB further down
+                    const uint32_t vb = v_s + s * Cfg::V_BYTES + kk * (16 * 128);
                     const uint64_t bdesc = ptx::smem_desc_sw128(vb, Cfg::KV_PANEL, 1024);
                     const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
                     if constexpr (Cfg::P_TMEM) {
@@ -240,6 +253,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_s = tmem + lane_base + Cfg::COL_S;
         const uint32_t t_o = tmem + lane_base + Cfg::COL_O;
         const uint32_t t_p = tmem + lane_base + Cfg::COL_P;
+        const float scale = p.scale_log2;
         float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
         float l = 0.f;
         bool ok = run;
@@ -253,54 +267,51 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ok = wait_all(s_full, (uint32_t)j & 1u);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
-            // pass 1: row maximum of the visible scores
-            float mx = -INFINITY;
+            // the whole row of S in registers, one wait; then S belongs to the MMA warp again
+            uint32_t sv[BN];
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld32(t_s + c * 32, v);
-                ptx::tmem_wait_ld();
-                if (need_mask) {
+            for (int c = 0; c < BN / 32; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+            ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = kv0 + c * 32 + i;
-                        const bool vis = col < kv_limit && (!p.causal || col <= row);
-                        mx = fmaxf(mx, vis ? __uint_as_float(v[i]) : -INFINITY);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
-            }
-            const float m_new = fmaxf(m_used, mx * p.scale_log2);
-            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
-            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
-            // pass 2: p = 2^(s*scale - m), row sum in fp32, pack to fp16 pairs
-            uint32_t pk[BN / 2];
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld32(t_s + c * 32, v);
-                ptx::tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float e0 = ptx::ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_next));
-                    float e1 = ptx::ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_next));
-                    if (need_mask) {
-                        const int col = kv0 + c * 32 + i;
-                        if (!(col < kv_limit && (!p.causal || col <= row))) e0 = 0.f;
-                        if (!(col + 1 < kv_limit && (!p.causal || col + 1 <= row))) e1 = 0.f;
-                    }
-                    sum += e0 + e1;
-                    pk[c * 16 + i / 2] = ptx::pack_half2(e0, e1);
-                }
-            }
-            // S has been read twice and is no longer needed: let QK^T of the next tile start
+            for (int c = 0; c < BN / 32; ++c) ptx::reg_fence32(&sv[c * 32]);
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive(s_free);
-            l = l * alpha + sum;
+
+            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int col = kv0 + i;
+                    const bool vis = col < kv_limit && (!p.causal || col <= row);
+                    if (!vis) sv[i] = 0xff800000u;       // -inf
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_new = fmaxf(m_used, mx * scale);
+            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+            uint32_t pk[BN / 2];
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                const float e0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), scale, -m_next));
+                const float e1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), scale, -m_next));
+                const float e2 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 2]), scale, -m_next));
+                const float e3 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 3]), scale, -m_next));
+                sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
+                pk[i / 2] = ptx::pack_half2(e0, e1);
+                pk[i / 2 + 1] = ptx::pack_half2(e2, e3);
+            }
+            l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
             m_used = m_next;
             if (j > 0) {
                 // PV of the previous tile must be finished before P is overwritten or O rescaled
@@ -309,10 +320,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 ptx::tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < DV / 32; ++c) {
                         uint32_t o[32];
                         ptx::tmem_ld32(t_o + c * 32, o);
                         ptx::tmem_wait_ld();
+                        ptx::reg_fence32(o);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         ptx::tmem_st32(t_o + c * 32, o);
@@ -322,12 +334,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             if constexpr (Cfg::P_TMEM) {
 #pragma unroll
-                for (int c = 0; c < BN / 64; ++c) {
-                    uint32_t t[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) t[i] = pk[c * 32 + i];
-                    ptx::tmem_st32(t_p + c * 32, t);
-                }
+                for (int c = 0; c < BN / 64; ++c) ptx::tmem_st32(t_p + c * 32, &pk[c * 32]);
+                if constexpr (BN % 64 == 32) ptx::tmem_st16(t_p + (BN / 64) * 32, &pk[(BN / 64) * 32]);
                 ptx::tmem_wait_st();
             } else {
                 // row r of P: BN/64 panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
@@ -347,12 +355,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (ok) {
                 ptx::tc_fence_after_sync();
                 const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
-                float *orow = p.out + ((size_t)bh * p.Sq + row) * D;
+                float *orow = p.out + ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < DV / 32; ++c) {
                     uint32_t o[32];
                     ptx::tmem_ld32(t_o + c * 32, o);
                     ptx::tmem_wait_ld();
+                    ptx::reg_fence32(o);
                     if (row < p.Sq) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
@@ -370,8 +379,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
         if (!run && *abort_flag == 0 && row < p.Sq) {
             // no visible key at all for this tile: the reference's 0/0
-            float *orow = p.out + ((size_t)bh * p.Sq + row) * D;
-            for (int i = 0; i < D; ++i) orow[i] = __int_as_float(0x7fc00000);
+            float *orow = p.out + ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
+            for (int i = 0; i < DV; ++i) orow[i] = __int_as_float(0x7fc00000);
         }
     }
 

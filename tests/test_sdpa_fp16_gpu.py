@@ -16,7 +16,7 @@ from tensorax_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 
-SS, TS = 0, _lib.TX_SDPA_P_IN_TMEM
+TS, SS = 0, _lib.TX_SDPA_P_IN_SMEM
 
 
 def widen(x):
@@ -69,7 +69,8 @@ def test_golden_grouped_heads_causal_key_lengths(golden):
 
 @pytest.mark.parametrize("flags", [SS, TS])
 @pytest.mark.parametrize("shape", [(1, 1, 1, 1, 64), (1, 2, 127, 129, 64), (2, 2, 128, 128, 128),
-                                   (1, 3, 300, 555, 128), (2, 1, 513, 64, 64), (1, 1, 80, 80, 64)])
+                                   (1, 3, 300, 555, 128), (2, 1, 513, 64, 64), (1, 1, 80, 80, 64),
+                                   (1, 2, 200, 333, 256), (2, 1, 129, 97, 512), (1, 1, 1, 31, 512)])
 def test_tensor_core_kernel_edge_shapes(flags, shape):
     B, H, Sq, Sk, d = shape
     q, k, v = (seeded(30 + j, B, H, S, d).astype(np.float16) for j, S in enumerate((Sq, Sk, Sk)))
@@ -78,7 +79,7 @@ def test_tensor_core_kernel_edge_shapes(flags, shape):
     assert_close_fp16(got, oracle.sdpa_f32(widen(q), widen(k), widen(v)))
 
 
-@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("d", [64, 128, 256, 512])
 def test_tensor_core_kernel_masks(d):
     B, Hq, Hkv, S = 3, 6, 2, 450
     q = seeded(40, B, Hq, S, d).astype(np.float16)
@@ -143,9 +144,13 @@ def test_config5_large_head_dims(d):
     B, H, S = 4, 8, 4096
     rng = np.random.Generator(np.random.PCG64(8))
     q, k, v = ((rng.standard_normal((B, H, S, d), dtype=np.float32) / np.sqrt(d)).astype(np.float16) for _ in range(3))
-    got, _ = sdpa_device(q, k, v)
+    got, tc = sdpa_device(q, k, v)
+    assert tc
     assert np.isfinite(got).all()
     check_sampled(got, q, k, v, [0, 17, B * H - 1], sample_rows(S, 4))
+    simt, tc = sdpa_device(q[:1, :2], k[:1, :2], v[:1, :2], flags=_lib.TX_SDPA_FORCE_SIMT)
+    assert not tc
+    assert np.abs(simt - got[:1, :2]).max() <= 2e-3
 
 
 def test_linearity_in_v_at_config2_size():
@@ -161,7 +166,8 @@ def test_linearity_in_v_at_config2_size():
     assert np.abs(os_ - (0.5 * o1 - 0.25 * o2)).max() <= 2e-3
 
 
-DETERMINISM = [(4, 8, 2048, 128), (4, 8, 4096, 128), (4, 8, 8192, 64), (1, 8, 8192, 64)]   # tests/test_sdpa_fp16.py:111-117
+DETERMINISM = [(4, 8, 2048, 128), (4, 8, 4096, 128), (4, 8, 8192, 64), (1, 8, 8192, 64),
+               (4, 8, 4096, 256)]   # tests/test_sdpa_fp16.py:111-117
 
 
 @pytest.mark.parametrize("cfg", DETERMINISM)
