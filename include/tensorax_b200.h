@@ -44,8 +44,11 @@ enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
 /* flags of tx_sdpa_desc */
 enum {
     TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
-    TX_SDPA_P_IN_SMEM = 2    /* tensor-core kernel: stage P in shared memory instead of tensor memory
+    TX_SDPA_P_IN_SMEM = 2,   /* tensor-core kernel: stage P in shared memory instead of tensor memory
                                 (ignored for d = 512, where shared memory has no room for it) */
+    TX_SDPA_EXP_F16X2 = 4    /* tensor-core kernel, d = 64 / 128: evaluate the exponentials two at a time in
+                                packed fp16 (the exponent is still formed in fp32, max and sum stay fp32);
+                                P is rounded to fp16 either way */
 };
 
 /* Message of the last failure on the calling thread ("" if none). */

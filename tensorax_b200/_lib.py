@@ -18,6 +18,7 @@ TX_DTYPE_F32 = 0
 TX_DTYPE_F16 = 1
 TX_SDPA_FORCE_SIMT = 1
 TX_SDPA_P_IN_SMEM = 2
+TX_SDPA_EXP_F16X2 = 4
 
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (

@@ -263,6 +263,15 @@ __device__ __forceinline__ void reg_fence32(uint32_t *r)
         :
         : "memory");
 }
+__device__ __forceinline__ void reg_fence16(uint32_t *r)
+{
+    asm volatile(""
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+          "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+          "+r"(r[14]), "+r"(r[15])
+        :
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -272,6 +281,27 @@ __device__ __forceinline__ float ex2_approx(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// two exponentials per special-function-unit operation: 2^x for both halves of a packed pair
+__device__ __forceinline__ uint32_t ex2_approx_f16x2(uint32_t x)
+{
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// acc (fp32) += both halves of a packed fp16 pair, each widened exactly
+__device__ __forceinline__ void add_half2_to_float(float &acc0, float &acc1, uint32_t h2)
+{
+    unsigned short lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(h2));
+    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc0) : "h"(lo));
+    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc1) : "h"(hi));
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
 {

@@ -199,11 +199,19 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
+    const bool exp16 = (d->flags & TX_SDPA_EXP_F16X2) != 0;
+    const bool nopf = (d->flags & 8) != 0;     // tuning switch: no next-tile prefetch
     switch (d->d_k) {
     case 64:
+        if (nopf && exp16) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, false>>(d, st, status);
+        if (nopf) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, false>>(d, st, status);
+        if (exp16) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
     case 128:
+        if (nopf && exp16) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true, false>>(d, st, status);
+        if (nopf) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, false>>(d, st, status);
+        if (exp16) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:

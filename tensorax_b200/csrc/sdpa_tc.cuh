@@ -54,8 +54,10 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool EXP16_ = false, bool PREFETCH_ = true>
 struct TcCfg {
+    static constexpr bool EXP16 = EXP16_; // exponentials evaluated two at a time in packed fp16
+    static constexpr bool PREFETCH = PREFETCH_;  // refill score registers with the next tile during the exponentials
     static constexpr int DK = DK_;        // head dim of Q and K
     static constexpr int DV = DV_;        // value columns this CTA owns
     static constexpr int BN = BN_;        // keys per tile
@@ -135,8 +137,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         ptx::mbar_init(q_full, 1);
         ptx::mbar_init(s_full, 1);
-        ptx::mbar_init(s_free, 128);
-        ptx::mbar_init(p_full, 128);
+        ptx::mbar_init(s_free, 4);     // one arrival per softmax warp
+        ptx::mbar_init(p_full, 4);
         ptx::mbar_init(pv_done, 1);
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(k_full + 8 * s, 1);
@@ -259,24 +261,55 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = run;
         // waits are made warp-uniform so that the .sync.aligned tensor-memory
         // instructions below are always executed by the whole warp
+        // One lane polls; the warp then converges, so the .sync.aligned tensor-memory
+        // instructions that follow are always executed by the whole warp.
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
-            return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+            int done = 1;
+            if (lane == 0) done = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+            done = __shfl_sync(0xffffffffu, done, 0);
+            __syncwarp();
+            return done != 0;
         };
+        // Every lane has fenced its own tensor-memory / shared-memory writes; one lane
+        // then arrives for the warp.
+        auto arrive_warp = [&](uint32_t bar) {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar);
+        };
+        constexpr int NCH = BN / 32;                      // 32-column chunks of a score row
+        constexpr int WAITC = NCH > 1 ? 1 : 0;            // chunk after which the next tile's S is awaited
+        // The score row of the current tile lives in registers.  While its chunks are
+        // exponentiated, the registers of finished chunks are refilled with the next
+        // tile's scores, so the tensor-memory read latency and the S hand-over hide
+        // behind the exponentials instead of standing between two tiles.
+        uint32_t sv[BN];
+        if (Cfg::PREFETCH && ok) {
+            ok = wait_all(s_full, 0);
+            if (ok) {
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
+                arrive_warp(s_free);
+            }
+        }
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int kv0 = j * BN;
-            ok = wait_all(s_full, (uint32_t)j & 1u);
-            if (!ok) break;
-            ptx::tc_fence_after_sync();
-            // the whole row of S in registers, one wait; then S belongs to the MMA warp again
-            uint32_t sv[BN];
+            const bool have_next = j + 1 < n_tiles;
+            if constexpr (!Cfg::PREFETCH) {
+                ok = wait_all(s_full, (uint32_t)j & 1u);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
-            ptx::tmem_wait_ld();
+                for (int c = 0; c < NCH; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                ptx::tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) ptx::reg_fence32(&sv[c * 32]);
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(s_free);
-
+                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
+                arrive_warp(s_free);
+            }
             const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
             if (need_mask) {
 #pragma unroll
@@ -286,32 +319,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     if (!vis) sv[i] = 0xff800000u;       // -inf
                 }
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int i = 0; i < BN; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+#ifdef TX_NO_MAX3
+                mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])));
+                mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])));
+#else
+                mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+#endif
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            const float m_new = fmaxf(m_used, mx * scale);
+            const float m_new = fmaxf(m_used, fmaxf(mx0, mx1) * scale);
             const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
             const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
-            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
-            uint32_t pk[BN / 2];
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < BN; i += 4) {
-                const float e0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), scale, -m_next));
-                const float e1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), scale, -m_next));
-                const float e2 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 2]), scale, -m_next));
-                const float e3 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 3]), scale, -m_next));
-                sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
-                pk[i / 2] = ptx::pack_half2(e0, e1);
-                pk[i / 2 + 1] = ptx::pack_half2(e2, e3);
-            }
-            l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
             m_used = m_next;
             if (j > 0) {
                 // PV of the previous tile must be finished before P is overwritten or O rescaled
@@ -319,36 +340,95 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-                    for (int c = 0; c < DV / 32; ++c) {
-                        uint32_t o[32];
-                        ptx::tmem_ld32(t_o + c * 32, o);
+                    // rare after the first tiles; 16 columns at a time, the score row stays in registers
+#pragma unroll 1
+                    for (int c = 0; c < DV / 16; ++c) {
+                        uint32_t o[16];
+                        ptx::tmem_ld16(t_o + c * 16, o);
                         ptx::tmem_wait_ld();
-                        ptx::reg_fence32(o);
+                        ptx::reg_fence16(o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        ptx::tmem_st32(t_o + c * 32, o);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st16(t_o + c * 16, o);
                     }
                     ptx::tmem_wait_st();
                 }
             }
-            if constexpr (Cfg::P_TMEM) {
+            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+            const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int c = 0; c < BN / 64; ++c) ptx::tmem_st32(t_p + c * 32, &pk[c * 32]);
-                if constexpr (BN % 64 == 32) ptx::tmem_st16(t_p + (BN / 64) * 32, &pk[(BN / 64) * 32]);
-                ptx::tmem_wait_st();
-            } else {
-                // row r of P: BN/64 panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
+            for (int c = 0; c < NCH; ++c) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int ch = 0; ch < BN / 8; ++ch) {
-                    const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
-                                          (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
-                    ptx::st_shared_v4(addr, pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                for (int i = 0; i < 32; i += 4) {
+#ifdef TX_NO_FFMA2
+                    const float2 xa = make_float2(fmaf(__uint_as_float(sv[c * 32 + i]), scale, -m_next),
+                                                  fmaf(__uint_as_float(sv[c * 32 + i + 1]), scale, -m_next));
+                    const float2 xb = make_float2(fmaf(__uint_as_float(sv[c * 32 + i + 2]), scale, -m_next),
+                                                  fmaf(__uint_as_float(sv[c * 32 + i + 3]), scale, -m_next));
+#else
+                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]),
+                                                             __uint_as_float(sv[c * 32 + i + 1])), scale2, negm2);
+                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i + 2]),
+                                                             __uint_as_float(sv[c * 32 + i + 3])), scale2, negm2);
+#endif
+                    if constexpr (Cfg::EXP16) {
+                        const uint32_t pa = ptx::ex2_approx_f16x2(ptx::pack_half2(xa.x, xa.y));
+                        const uint32_t pb = ptx::ex2_approx_f16x2(ptx::pack_half2(xb.x, xb.y));
+                        ptx::add_half2_to_float(sum_a.x, sum_a.y, pa);   // l sums exactly the P that PV uses
+                        ptx::add_half2_to_float(sum_b.x, sum_b.y, pb);
+                        pk[i / 2] = pa;
+                        pk[i / 2 + 1] = pb;
+                    } else {
+                        const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                        const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+#ifdef TX_NO_FFMA2
+                        sum_a.x += ea.x; sum_a.y += ea.y; sum_b.x += eb.x; sum_b.y += eb.y;
+#else
+                        sum_a = __fadd2_rn(sum_a, ea);
+                        sum_b = __fadd2_rn(sum_b, eb);
+#endif
+                        pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                        pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+                    }
                 }
-                ptx::fence_proxy_async_smem();
+                if constexpr (Cfg::P_TMEM) {
+                    ptx::tmem_st16(t_p + c * 16, pk);
+                } else {
+                    // row r of P: 64-column panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int ch = c * 4 + q;
+                        const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
+                                              (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
+                        ptx::st_shared_v4(addr, pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+                    }
+                }
+                // refill finished chunks with the next tile's scores
+                if (Cfg::PREFETCH && have_next && c >= WAITC) {
+                    if (c == WAITC) {
+                        ok = wait_all(s_full, (uint32_t)(j + 1) & 1u);
+                        if (!ok) break;
+                        ptx::tc_fence_after_sync();
+#pragma unroll
+                        for (int cc = 0; cc <= WAITC; ++cc) ptx::tmem_ld32(t_s + cc * 32, &sv[cc * 32]);
+                    } else {
+                        ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                    }
+                }
             }
-            ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(p_full);
+            if (!ok) break;
+            l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+            if constexpr (Cfg::P_TMEM) ptx::tmem_wait_st();
+            else ptx::fence_proxy_async_smem();
+            arrive_warp(p_full);
+            if (Cfg::PREFETCH && have_next) {
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
+                arrive_warp(s_free);           // S of tile j+1 is in registers: QK^T of tile j+2 may start
+            }
         }
         if (run && ok) {
             ok = wait_all(pv_done, (uint32_t)(n_tiles - 1) & 1u);
