@@ -44,11 +44,8 @@ enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
 /* flags of tx_sdpa_desc */
 enum {
     TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
-    TX_SDPA_P_IN_SMEM = 2,   /* tensor-core kernel: stage P in shared memory instead of tensor memory
+    TX_SDPA_P_IN_SMEM = 2    /* tensor-core kernel: stage P in shared memory instead of tensor memory
                                 (ignored for d = 512, where shared memory has no room for it) */
-    TX_SDPA_EXP_F16X2 = 4    /* tensor-core kernel, d = 64 / 128: evaluate the exponentials two at a time in
-                                packed fp16 (the exponent is still formed in fp32, max and sum stay fp32);
-                                P is rounded to fp16 either way */
 };
 
 /* Message of the last failure on the calling thread ("" if none). */
@@ -139,6 +136,17 @@ TX_API int tx_sdpa_finish(void *stream);
 TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
 /* How many kernels of this library have been launched by this process so far. */
 TX_API int64_t tx_kernel_launch_count(void);
+
+/* ---- section profile: reference csrc/tensor_ops.cpp:1434-1507 (profile_sections_sdpa_*) over the
+ *      TX_TICK clock64 sections of csrc/cuda/profiling.cuh:20-51.  Runs `desc` once on an instrumented
+ *      build of the tensor-core kernel (d = 64 or 128) and returns 32 cycle counters of CTA (0,0,0),
+ *      summed over its key tiles.  Softmax lane: [0] loop total, [1] wait for S, [2] S -> registers,
+ *      [3] mask + row max, [5] exponentials + pack + sum,
+ *      [6] wait for the previous PV, [7] O rescale, [8] P store + hand-over, [9] epilogue, [10] tiles.
+ *      MMA lane: [16] loop total, [17] wait for S to be consumed, [18] K wait + QK^T issue,
+ *      [19] wait for V, [20] wait for P, [21] PV issue.  Producer lane: [24] total, [25] wait for a
+ *      free K stage, [26] wait for a free V stage. */
+TX_API int tx_profile_sections_sdpa(const tx_sdpa_desc *desc, long long *ticks32);
 
 /* ---- host-buffer form (no reference counterpart): `desc` holds HOST pointers
  *      (q, k, v, kv_lens, out; mask must be NULL).  Copies in, runs, copies out,

@@ -18,7 +18,6 @@ TX_DTYPE_F32 = 0
 TX_DTYPE_F16 = 1
 TX_SDPA_FORCE_SIMT = 1
 TX_SDPA_P_IN_SMEM = 2
-TX_SDPA_EXP_F16X2 = 4
 
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (
@@ -30,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_optimized_flash_cuda", "tx_sdpa_mma_cuda", "tx_sdpa_mma_fp16_cuda",
     "tx_cast_f32_to_f16_cuda", "tx_repeat_interleave_cuda",
     "tx_sdpa_forward", "tx_sdpa_finish", "tx_sdpa_uses_tensor_cores",
-    "tx_kernel_launch_count", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
+    "tx_kernel_launch_count", "tx_profile_sections_sdpa", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
 )
 
 
@@ -85,6 +84,7 @@ def load():
     lib.tx_cast_f32_to_f16_cuda.argtypes = [c_void_p, c_void_p, c_int64]
     lib.tx_repeat_interleave_cuda.argtypes = [c_void_p, c_void_p] + [c_int64] * 4 + [c_int32]
     lib.tx_sdpa_forward.argtypes = [ctypes.POINTER(SdpaDesc)]
+    lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_uses_tensor_cores.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_finish.argtypes = [c_void_p]

@@ -154,6 +154,26 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
     return d;
 }
 
+// The same descriptor split for cheap address arithmetic by the issuing thread: the
+// upper word and the non-address bits of the lower word are constants of the layout,
+// the start address only fills bits 0-13 of the lower word, so moving the start by
+// `bytes` is one 32-bit add of bytes >> 4 (addresses stay below 256 KB: no carry
+// into the next field).
+__host__ __device__ constexpr uint32_t smem_desc_sw128_hi(uint32_t sbo_bytes)
+{
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t addr, uint32_t lbo_bytes)
+{
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi)
+{
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor, kind::f16, fp16 A and B, fp32 accumulator.
 //   bits 4-5 D format (1 = f32), 7-9 A format (0 = f16), 10-12 B format,
 //   bit 15 A major (0 = K), bit 16 B major (0 = K, 1 = MN),
@@ -249,6 +269,22 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r)
           "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// 8-column forms
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
 // Ties 32 registers to this point of the instruction stream.  tcgen05.ld fills its
 // destination registers asynchronously; placing this after tcgen05.wait::ld keeps the
 // compiler from scheduling a use of those registers ahead of the wait.
@@ -272,6 +308,46 @@ __device__ __forceinline__ void reg_fence16(uint32_t *r)
         :
         : "memory");
 }
+__device__ __forceinline__ void reg_fence8(uint32_t *r)
+{
+    asm volatile(""
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+        :
+        : "memory");
+}
+// N consecutive columns (N = 8, 16 or a multiple of 32) of this thread's lane
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r)
+{
+    static_assert(N == 8 || N == 16 || N % 32 == 0, "unsupported column count");
+    if constexpr (N == 8) tmem_ld8(taddr, r);
+    else if constexpr (N == 16) tmem_ld16(taddr, r);
+    else {
+#pragma unroll
+        for (int c = 0; c < N / 32; ++c) tmem_ld32(taddr + c * 32, r + c * 32);
+    }
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t *r)
+{
+    static_assert(N == 8 || N == 16 || N % 32 == 0, "unsupported column count");
+    if constexpr (N == 8) tmem_st8(taddr, r);
+    else if constexpr (N == 16) tmem_st16(taddr, r);
+    else {
+#pragma unroll
+        for (int c = 0; c < N / 32; ++c) tmem_st32(taddr + c * 32, r + c * 32);
+    }
+}
+template <int N>
+__device__ __forceinline__ void reg_fence_cols(uint32_t *r)
+{
+    if constexpr (N == 8) reg_fence8(r);
+    else if constexpr (N == 16) reg_fence16(r);
+    else {
+#pragma unroll
+        for (int c = 0; c < N / 32; ++c) reg_fence32(r + c * 32);
+    }
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -282,26 +358,11 @@ __device__ __forceinline__ float ex2_approx(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// two exponentials per special-function-unit operation: 2^x for both halves of a packed pair
-__device__ __forceinline__ uint32_t ex2_approx_f16x2(uint32_t x)
-{
-    uint32_t y;
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
-}
 __device__ __forceinline__ float max3(float a, float b, float c)
 {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-}
-// acc (fp32) += both halves of a packed fp16 pair, each widened exactly
-__device__ __forceinline__ void add_half2_to_float(float &acc0, float &acc1, uint32_t h2)
-{
-    unsigned short lo, hi;
-    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(h2));
-    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc0) : "h"(lo));
-    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc1) : "h"(hi));
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
 {

@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -166,7 +167,7 @@ int launch_simt(const txb::SimtParams &p, cudaStream_t st)
 }
 
 template <class Cfg>
-int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
 {
     CUtensorMap tq, tk, tv;
     if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, d->d_k, Cfg::BM)) return rc;
@@ -183,6 +184,7 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
     p.dv_total = (int)d->d_v;
     p.causal = d->causal ? 1 : 0;
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
+    p.prof = prof;
     TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::SMEM_BYTES));
     dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads),
@@ -199,19 +201,17 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
-    const bool exp16 = (d->flags & TX_SDPA_EXP_F16X2) != 0;
-    const bool nopf = (d->flags & 8) != 0;     // tuning switch: no next-tile prefetch
+    const int tune = (d->flags >> 3) & 7;     // tuning switch while the pipelined loop is characterised
     switch (d->d_k) {
     case 64:
-        if (nopf && exp16) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, false>>(d, st, status);
-        if (nopf) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, false>>(d, st, status);
-        if (exp16) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status);
+        if (tune == 1) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 3>>(d, st, status);
+        if (tune == 2) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 2>>(d, st, status);
+        if (tune == 4) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 4>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
     case 128:
-        if (nopf && exp16) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true, false>>(d, st, status);
-        if (nopf) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, false>>(d, st, status);
-        if (exp16) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status);
+        if (tune == 1) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 1>>(d, st, status);
+        if (tune == 2) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 2>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:
@@ -527,6 +527,36 @@ int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t 
 }
 
 int tx_sdpa_forward(const tx_sdpa_desc *desc) { return forward(desc); }
+
+int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
+{
+    if (!ticks32) return fail(TX_ERR_INVALID, "profile_sections: null output");
+    if (int rc = validate(d)) return rc;
+    if (!tc_eligible(d) || (d->d_k != 64 && d->d_k != 128))
+        return fail(TX_ERR_UNSUPPORTED, "profile_sections: built for the tensor-core kernel at d = 64 and d = 128");
+    if (int rc = ensure_device()) return rc;
+    int *status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    long long *dev = nullptr;
+    TX_CUDA(cudaMalloc(&dev, 32 * sizeof(long long)));
+    cudaStream_t st = static_cast<cudaStream_t>(d->stream);
+    int rc = TX_OK;
+    if (cudaMemsetAsync(dev, 0, 32 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
+    if (rc == TX_OK) {
+        const int tune = (d->flags >> 3) & 7;
+        if (d->d_k == 64)
+            rc = tune == 1 ? launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, 3>>(d, st, status, dev)
+                           : launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status, dev);
+        else
+            rc = tune == 1 ? launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true, 1>>(d, st, status, dev)
+                           : launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
+    }
+    if (rc == TX_OK) rc = finish(st);
+    if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        rc = fail(TX_ERR_CUDA, "cudaMemcpy of the section profile failed");
+    (void)cudaFree(dev);
+    return rc;
+}
 
 int tx_sdpa_finish(void *stream) { return finish(static_cast<cudaStream_t>(stream)); }
 

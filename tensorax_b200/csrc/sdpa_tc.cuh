@@ -13,21 +13,25 @@
 // value columns (the slice is the whole head except for d = 512, where two CTAs
 // each recompute S and own 256 output columns, as the reference's D_V_PASSES does
 // in sequence, attn.cu:1239-1241).  Six warps:
-//   warp 0      TMA producer (one lane): Q once, then K/V tiles through an
-//               NS-deep ring of shared-memory stages, 128-byte swizzled
-//   warp 1      owns tensor memory (alloc/dealloc); one lane issues every MMA:
+//   warp 0      TMA producer: Q once, then K/V tiles through an NS-deep ring of
+//               shared-memory stages, 128-byte swizzled
+//   warp 1      owns tensor memory (alloc/dealloc) and issues every MMA:
 //               S = Q K^T (M=128, N=BN, K=16 per instruction) and
 //               O += P V  (M=128, N=DV, K=16 per instruction, V read MN-major)
+//               Both warps keep their control flow warp-uniform and elect one lane
+//               only for the issue instructions, so descriptors, coordinates and
+//               barrier handles stay in uniform registers (issuing from a divergent
+//               single lane cost ~75 extra cycles per MMA).
 //   warps 2-5   softmax: thread t owns query row 32*(warp%4)+lane, the tensor
 //               memory lane it is allowed to read.  The whole S row is pulled into
-//               registers with one wait, S is handed back to the MMA warp at once,
-//               then: masks in registers, row max, exp2, fp16 pack, P written to
-//               tensor memory (or swizzled shared memory).  O is rescaled in tensor
-//               memory only when the running max grew by more than 2^8; the epilogue
-//               writes O/l as fp32.
+//               registers with one wait and S is handed back to the MMA warp at
+//               once; then masks in registers, row max, exp2 (two-wide fp32 FMAs
+//               form the exponents), fp16 pack, P written to tensor memory (or
+//               swizzled shared memory).  O is rescaled in tensor memory only when
+//               the running max grew by more than 2^8; the epilogue writes O/l as
+//               fp32.
 // For d <= 128 two such CTAs fit one SM (shared memory <= 113 KB, 256
-// tensor-memory columns, <= 168 registers), so one CTA's softmax overlaps the
-// other's MMAs.
+// tensor-memory columns), so one CTA's softmax overlaps the other's MMAs.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in
 // `status` and the whole CTA drains and frees its tensor memory.
@@ -44,6 +48,18 @@ struct TcParams {
     int dv_total;             // row length of `out` (= DV * gridDim.z)
     int causal;
     float scale_log2;         // (1/sqrt(d_k)) * log2(e)
+    long long *prof;          // optional [32] cycle counters written by CTA (0,0,0) (section profile)
+};
+
+// Section profile (the counterpart of the reference's TX_TICK clock64 sections,
+// csrc/cuda/profiling.cuh:20-51): cycles one softmax lane, the MMA lane and the
+// producer lane of CTA (0,0,0) spend in each step of their loops, summed over tiles.
+enum TcSection : int {
+    SEC_SM_TOTAL = 0, SEC_SM_WAIT_S = 1, SEC_SM_LOAD_S = 2, SEC_SM_MAX = 3, SEC_SM_EXP = 5,
+    SEC_SM_WAIT_PV = 6, SEC_SM_RESCALE = 7, SEC_SM_STORE_P = 8, SEC_SM_EPILOGUE = 9, SEC_SM_TILES = 10,
+    SEC_MMA_TOTAL = 16, SEC_MMA_WAIT_SFREE = 17, SEC_MMA_QK = 18, SEC_MMA_WAIT_V = 19, SEC_MMA_WAIT_P = 20,
+    SEC_MMA_PV = 21,
+    SEC_LD_TOTAL = 24, SEC_LD_WAIT_K = 25, SEC_LD_WAIT_V = 26,
 };
 
 enum TcStatus : int {
@@ -54,17 +70,21 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool EXP16_ = false, bool PREFETCH_ = true>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int PIPE_ = 0>
 struct TcCfg {
-    static constexpr bool EXP16 = EXP16_; // exponentials evaluated two at a time in packed fp16
-    static constexpr bool PREFETCH = PREFETCH_;  // refill score registers with the next tile during the exponentials
+    static constexpr bool PROF = PROF_;   // collect the section profile
+    // PIPE > 0: the softmax loop refills the registers of finished 32-column chunks with the next
+    // tile's scores while the remaining chunks are exponentiated; the next tile's S is awaited after
+    // chunk PIPE-1.  PIPE = 0: load, max, exponentiate, store, one after the other.
+    static constexpr int PIPE = PIPE_;
     static constexpr int DK = DK_;        // head dim of Q and K
     static constexpr int DV = DV_;        // value columns this CTA owns
     static constexpr int BN = BN_;        // keys per tile
     static constexpr int NS = NS_;        // K/V ring depth
     static constexpr bool P_TMEM = P_TMEM_;
     static constexpr int BM = 128;        // query rows per CTA
-    static constexpr int THREADS = 192;
+    static constexpr int SOFTMAX_WARPS = 4;
+    static constexpr int THREADS = 64 + 32 * SOFTMAX_WARPS;
     static constexpr int KP = DK / 64;    // 64-column (128-byte) panels per row of Q / K
     static constexpr int VP = DV / 64;    // panels per row of this CTA's V slice
     static constexpr uint32_t Q_BYTES = BM * DK * 2;
@@ -92,6 +112,7 @@ struct TcCfg {
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
     static_assert(DK % 64 == 0 && DV % 64 == 0, "panels are 64 columns wide");
     static_assert(BN % 32 == 0 && (P_TMEM || BN % 64 == 0), "P in shared memory needs 64-column panels");
+    static_assert(PIPE == 0 || (P_TMEM && PIPE <= BN / 32), "the pipelined loop stores P to tensor memory chunk by chunk");
     static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
     static_assert(BN <= 256 && DV <= 256, "one MMA instruction covers N <= 256");
     static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA may have");
@@ -120,6 +141,24 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // section profile: `tick(i)` adds the cycles since the previous tick to counter i
+    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    long long prof_last = 0;
+    long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    auto tick = [&](int i) {
+        if constexpr (Cfg::PROF) {
+            if (prof_on) {
+                const long long now = clock64();
+                prof_acc[i] += now - prof_last;
+                prof_last = now;
+            }
+        }
+    };
+    auto tick_start = [&]() {
+        if constexpr (Cfg::PROF) {
+            if (prof_on) prof_last = clock64();
+        }
+    };
     const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) causal tiles first
     const int q0 = q_tile * BM;
     const int bh = blockIdx.y;
@@ -137,8 +176,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         ptx::mbar_init(q_full, 1);
         ptx::mbar_init(s_full, 1);
-        ptx::mbar_init(s_free, 4);     // one arrival per softmax warp
-        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(s_free, Cfg::SOFTMAX_WARPS);     // one arrival per softmax warp
+        ptx::mbar_init(p_full, Cfg::SOFTMAX_WARPS);
         ptx::mbar_init(pv_done, 1);
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(k_full + 8 * s, 1);
@@ -159,92 +198,156 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_p = tmem + Cfg::COL_P;
     const bool run = (*abort_flag == 0) && n_tiles > 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0 && run) {
-            ptx::prefetch_tmap(&tm_q);
-            ptx::prefetch_tmap(&tm_k);
-            ptx::prefetch_tmap(&tm_v);
-            ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-            for (int pn = 0; pn < Cfg::KP; ++pn)
-                ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+        // The whole warp walks the loop with identical values (so addresses, coordinates and
+        // barrier handles stay in uniform registers); one elected lane issues the copies.
+        if (run) {
+            const bool leader = ptx::elect_one();
+            if (leader) {
+                ptx::prefetch_tmap(&tm_q);
+                ptx::prefetch_tmap(&tm_k);
+                ptx::prefetch_tmap(&tm_v);
+                ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+                for (int pn = 0; pn < Cfg::KP; ++pn)
+                    ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+            }
+            __syncwarp();
             bool ok = true;
+            tick_start();
+            const long long t_begin = Cfg::PROF ? clock64() : 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                tick(0);
                 ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
+                tick(1);
                 if (!ok) break;
-                ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
-                for (int pn = 0; pn < Cfg::KP; ++pn)
-                    ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
-                                     k_full + 8 * s, pn * 64, j * BN, kvh);
+                if (leader) {
+                    ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
+                                         k_full + 8 * s, pn * 64, j * BN, kvh);
+                }
+                __syncwarp();
+                tick(0);
                 ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                tick(2);
                 if (!ok) break;
-                ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
-                for (int pn = 0; pn < Cfg::VP; ++pn)
-                    ptx::tma_load_3d(v_s + s * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
-                                     v_full + 8 * s, dv0 + pn * 64, j * BN, kvh);
+                if (leader) {
+                    ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::VP; ++pn)
+                        ptx::tma_load_3d(v_s + s * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                         v_full + 8 * s, dv0 + pn * 64, j * BN, kvh);
+                }
+                __syncwarp();
             }
-            if (!ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
+            if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
+            if constexpr (Cfg::PROF) {
+                if (prof_on && leader) {
+                    p.prof[SEC_LD_TOTAL] = clock64() - t_begin;
+                    p.prof[SEC_LD_WAIT_K] = prof_acc[1];
+                    p.prof[SEC_LD_WAIT_V] = prof_acc[2];
+                }
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && run) {
+        // Warp-uniform control flow (descriptors live in uniform registers); one elected lane,
+        // the same one every time, issues the MMAs and the commits that track them.
+        if (run) {
+            const bool leader = ptx::elect_one();
             constexpr uint32_t idesc_qk = ptx::idesc_f16(BM, BN, false);
             constexpr uint32_t idesc_pv = ptx::idesc_f16(BM, DV, true);
-            const uint32_t t_s = tmem + Cfg::COL_S, t_o = tmem + Cfg::COL_O, t_p = tmem + Cfg::COL_P;
+            const uint32_t t_s = tmem + Cfg::COL_S, t_o = tmem + Cfg::COL_O, t_p = tmem_p;
+            // Descriptors are formed once; inside the loops a descriptor is one 32-bit add away.
+            constexpr uint32_t desc_hi = ptx::smem_desc_sw128_hi(1024);
+            const uint32_t q_lo = ptx::smem_desc_sw128_lo(q_s, 16);
+            const uint32_t k_lo = ptx::smem_desc_sw128_lo(k_s, 16);
+            const uint32_t v_lo = ptx::smem_desc_sw128_lo(v_s, Cfg::KV_PANEL);
+            const uint32_t p_lo = ptx::smem_desc_sw128_lo(p_s, 16);
             bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
                 if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag)) return false;
                 ptx::tc_fence_after_sync();
+                const uint32_t ks_lo = k_lo + (uint32_t)s * (Cfg::K_BYTES >> 4);
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < DK / 16; ++kk) {
-                    const uint32_t a = q_s + (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-                    const uint32_t bb = k_s + s * Cfg::K_BYTES + (kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32;
-                    ptx::mma_ss(t_s, ptx::smem_desc_sw128(a, 16, 1024),
-                                ptx::smem_desc_sw128(bb, 16, 1024), idesc_qk, kk > 0);
+                    for (int kk = 0; kk < DK / 16; ++kk) {
+                        const uint32_t qa = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+                        const uint32_t kb = ((kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32) >> 4;
+                        ptx::mma_ss(t_s, ptx::make_desc(q_lo + qa, desc_hi), ptx::make_desc(ks_lo + kb, desc_hi),
+                                    idesc_qk, kk > 0);
+                    }
+                    ptx::mma_commit(k_empty + 8 * s);
+                    ptx::mma_commit(s_full);
                 }
-                ptx::mma_commit(k_empty + 8 * s);
-                ptx::mma_commit(s_full);
+                __syncwarp();
                 return true;
             };
             if (ok) ok = issue_qk(0);
+            tick_start();
+            const long long t_begin = Cfg::PROF ? clock64() : 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
+                    tick(0);
                     ok = ptx::mbar_wait(s_free, (uint32_t)j & 1u, abort_flag);
+                    tick(1);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
                     ok = issue_qk(j + 1);
+                    tick(2);
                     if (!ok) break;
                 }
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                tick(0);
                 ok = ptx::mbar_wait(v_full + 8 * s, ph, abort_flag);
+                tick(3);
                 if (!ok) break;
                 ok = ptx::mbar_wait(p_full, (uint32_t)j & 1u, abort_flag);
+                tick(4);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
+                const uint32_t vs_lo = v_lo + (uint32_t)s * (Cfg::V_BYTES >> 4);
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    // V stage: DV/64 panels of [BN keys][64 cols]; 16 keys = 2 KB further down
-                    const uint32_t vb = v_s + s * Cfg::V_BYTES + kk * (16 * 128);
-                    const uint64_t bdesc = ptx::smem_desc_sw128(vb, Cfg::KV_PANEL, 1024);
-                    const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-                    if constexpr (Cfg::P_TMEM) {
-                        ptx::mma_ts(t_o, t_p + kk * 8, bdesc, idesc_pv, acc);
-                    } else {
-                        const uint32_t pa = p_s + (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-                        ptx::mma_ss(t_o, ptx::smem_desc_sw128(pa, 16, 1024), bdesc, idesc_pv, acc);
+                    for (int kk = 0; kk < BN / 16; ++kk) {
+                        // V stage: DV/64 panels of [BN keys][64 cols]; 16 keys = 2 KB further down
+                        const uint64_t bdesc = ptx::make_desc(vs_lo + kk * ((16 * 128) >> 4), desc_hi);
+                        const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (Cfg::P_TMEM) {
+                            ptx::mma_ts(t_o, t_p + kk * 8, bdesc, idesc_pv, acc);
+                        } else {
+                            const uint32_t pa = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+                            ptx::mma_ss(t_o, ptx::make_desc(p_lo + pa, desc_hi), bdesc, idesc_pv, acc);
+                        }
                     }
+                    ptx::mma_commit(v_empty + 8 * s);
+                    ptx::mma_commit(pv_done);
                 }
-                ptx::mma_commit(v_empty + 8 * s);
-                ptx::mma_commit(pv_done);
+                __syncwarp();
+                tick(5);
             }
-            if (!ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_MMA); }
+            if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_MMA); }
+            if constexpr (Cfg::PROF) {
+                if (prof_on && leader) {
+                    p.prof[SEC_MMA_TOTAL] = clock64() - t_begin;
+                    p.prof[SEC_MMA_WAIT_SFREE] = prof_acc[1];
+                    p.prof[SEC_MMA_QK] = prof_acc[2];
+                    p.prof[SEC_MMA_WAIT_V] = prof_acc[3];
+                    p.prof[SEC_MMA_WAIT_P] = prof_acc[4];
+                    p.prof[SEC_MMA_PV] = prof_acc[5];
+                }
+            }
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue
@@ -254,13 +357,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem + lane_base + Cfg::COL_S;
         const uint32_t t_o = tmem + lane_base + Cfg::COL_O;
-        const uint32_t t_p = tmem + lane_base + Cfg::COL_P;
+        const uint32_t t_p = tmem_p + lane_base;
         const float scale = p.scale_log2;
         float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
         float l = 0.f;
         bool ok = run;
-        // waits are made warp-uniform so that the .sync.aligned tensor-memory
-        // instructions below are always executed by the whole warp
         // One lane polls; the warp then converges, so the .sync.aligned tensor-memory
         // instructions that follow are always executed by the whole warp.
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
@@ -277,159 +378,240 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar);
         };
-        constexpr int NCH = BN / 32;                      // 32-column chunks of a score row
-        constexpr int WAITC = NCH > 1 ? 1 : 0;            // chunk after which the next tile's S is awaited
-        // The score row of the current tile lives in registers.  While its chunks are
-        // exponentiated, the registers of finished chunks are refilled with the next
-        // tile's scores, so the tensor-memory read latency and the S hand-over hide
-        // behind the exponentials instead of standing between two tiles.
-        uint32_t sv[BN];
-        if (Cfg::PREFETCH && ok) {
-            ok = wait_all(s_full, 0);
-            if (ok) {
-                ptx::tc_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
-                ptx::tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
-                arrive_warp(s_free);
-            }
-        }
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int kv0 = j * BN;
-            const bool have_next = j + 1 < n_tiles;
-            if constexpr (!Cfg::PREFETCH) {
+        tick_start();
+        const long long t_begin = Cfg::PROF ? clock64() : 0;
+        if constexpr (Cfg::PIPE == 0) {
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int kv0 = j * BN;
+                tick(0);
                 ok = wait_all(s_full, (uint32_t)j & 1u);
+                tick(SEC_SM_WAIT_S);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                // this thread's part of the S row in registers, one wait; then S belongs to the MMA warp again
+                uint32_t sv[BN];
+                ptx::tmem_ld_cols<BN>(t_s, sv);
                 ptx::tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
+                ptx::reg_fence_cols<BN>(sv);
                 arrive_warp(s_free);
-            }
-            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
-            if (need_mask) {
-#pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int col = kv0 + i;
-                    const bool vis = col < kv_limit && (!p.causal || col <= row);
-                    if (!vis) sv[i] = 0xff800000u;       // -inf
-                }
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < BN; i += 4) {
-#ifdef TX_NO_MAX3
-                mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])));
-                mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])));
-#else
-                mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-                mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
-#endif
-            }
-            const float m_new = fmaxf(m_used, fmaxf(mx0, mx1) * scale);
-            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
-            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
-            m_used = m_next;
-            if (j > 0) {
-                // PV of the previous tile must be finished before P is overwritten or O rescaled
-                ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
-                if (!ok) break;
-                ptx::tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                    // rare after the first tiles; 16 columns at a time, the score row stays in registers
-#pragma unroll 1
-                    for (int c = 0; c < DV / 16; ++c) {
-                        uint32_t o[16];
-                        ptx::tmem_ld16(t_o + c * 16, o);
-                        ptx::tmem_wait_ld();
-                        ptx::reg_fence16(o);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        ptx::tmem_st16(t_o + c * 16, o);
+                tick(SEC_SM_LOAD_S);
+
+                const bool need_mask = (j * BN + BN > kv_limit) || (p.causal && (j * BN + BN - 1 > q0));
+                if (need_mask) {
+    #pragma unroll
+                    for (int i = 0; i < BN; ++i) {
+                        const int col = kv0 + i;
+                        const bool vis = col < kv_limit && (!p.causal || col <= row);
+                        if (!vis) sv[i] = 0xff800000u;       // -inf
                     }
-                    ptx::tmem_wait_st();
                 }
-            }
-            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
-            const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
-            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-#ifdef TX_NO_FFMA2
-                    const float2 xa = make_float2(fmaf(__uint_as_float(sv[c * 32 + i]), scale, -m_next),
-                                                  fmaf(__uint_as_float(sv[c * 32 + i + 1]), scale, -m_next));
-                    const float2 xb = make_float2(fmaf(__uint_as_float(sv[c * 32 + i + 2]), scale, -m_next),
-                                                  fmaf(__uint_as_float(sv[c * 32 + i + 3]), scale, -m_next));
-#else
-                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]),
-                                                             __uint_as_float(sv[c * 32 + i + 1])), scale2, negm2);
-                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i + 2]),
-                                                             __uint_as_float(sv[c * 32 + i + 3])), scale2, negm2);
-#endif
-                    if constexpr (Cfg::EXP16) {
-                        const uint32_t pa = ptx::ex2_approx_f16x2(ptx::pack_half2(xa.x, xa.y));
-                        const uint32_t pb = ptx::ex2_approx_f16x2(ptx::pack_half2(xb.x, xb.y));
-                        ptx::add_half2_to_float(sum_a.x, sum_a.y, pa);   // l sums exactly the P that PV uses
-                        ptx::add_half2_to_float(sum_b.x, sum_b.y, pb);
-                        pk[i / 2] = pa;
-                        pk[i / 2 + 1] = pb;
-                    } else {
-                        const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
-                        const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
-#ifdef TX_NO_FFMA2
-                        sum_a.x += ea.x; sum_a.y += ea.y; sum_b.x += eb.x; sum_b.y += eb.y;
-#else
-                        sum_a = __fadd2_rn(sum_a, ea);
-                        sum_b = __fadd2_rn(sum_b, eb);
-#endif
-                        pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
-                        pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+    #pragma unroll
+                for (int i = 0; i < BN; i += 8) {
+                    mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                    mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                    mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                    mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                tick(SEC_SM_MAX);
+                const float m_new = fmaxf(m_used, mx * scale);
+                const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+                const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+                m_used = m_next;
+                // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+                const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+                uint32_t pk[BN / 2];
+    #pragma unroll
+                for (int i = 0; i < BN; i += 4) {
+                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
+                                                 scale2, negm2);
+                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
+                                                 scale2, negm2);
+                    const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                    const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                    sum_a = __fadd2_rn(sum_a, ea);
+                    sum_b = __fadd2_rn(sum_b, eb);
+                    pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                    pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+                }
+                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+                tick(SEC_SM_EXP);
+                if (j > 0) {
+                    // PV of the previous tile must be finished before P is overwritten or O rescaled
+                    ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
+                    tick(SEC_SM_WAIT_PV);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                        // rare after the first tiles; 16 columns at a time so the score row stays in registers
+    #pragma unroll 1
+                        for (int c = 0; c < DV / 16; ++c) {
+                            uint32_t o[16];
+                            ptx::tmem_ld16(t_o + c * 16, o);
+                            ptx::tmem_wait_ld();
+                            ptx::reg_fence16(o);
+    #pragma unroll
+                            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            ptx::tmem_st16(t_o + c * 16, o);
+                        }
+                        ptx::tmem_wait_st();
                     }
+                    tick(SEC_SM_RESCALE);
                 }
                 if constexpr (Cfg::P_TMEM) {
-                    ptx::tmem_st16(t_p + c * 16, pk);
+                    ptx::tmem_st_cols<BN / 2>(t_p, pk);
+                    ptx::tmem_wait_st();
                 } else {
                     // row r of P: 64-column panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int ch = c * 4 + q;
+    #pragma unroll
+                    for (int q = 0; q < BN / 8; ++q) {
+                        const int ch = q;
                         const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
                                               (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
                         ptx::st_shared_v4(addr, pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
                     }
+                    ptx::fence_proxy_async_smem();
                 }
-                // refill finished chunks with the next tile's scores
-                if (Cfg::PREFETCH && have_next && c >= WAITC) {
-                    if (c == WAITC) {
-                        ok = wait_all(s_full, (uint32_t)(j + 1) & 1u);
-                        if (!ok) break;
-                        ptx::tc_fence_after_sync();
+                arrive_warp(p_full);
+                tick(SEC_SM_STORE_P);
+            }
+        } else {
+            // ---- pipelined form.  Invariant at the top of iteration j: sv holds row r of S(j), masked,
+            // and mx is its maximum; S in tensor memory already belongs to the MMA warp again.
+            constexpr int NCH = BN / 32;
+            constexpr int WAITC = Cfg::PIPE - 1;
+            uint32_t sv[BN];
+            float mx = -INFINITY;
+            auto mask_chunk = [&](int j_tile, int c) {
+                const int kv0 = j_tile * BN;
+                const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
+                if (need_mask) {
 #pragma unroll
-                        for (int cc = 0; cc <= WAITC; ++cc) ptx::tmem_ld32(t_s + cc * 32, &sv[cc * 32]);
-                    } else {
-                        ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = kv0 + c * 32 + i;
+                        const bool vis = col < kv_limit && (!p.causal || col <= row);
+                        if (!vis) sv[c * 32 + i] = 0xff800000u;       // -inf
                     }
                 }
-            }
-            if (!ok) break;
-            l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
-            if constexpr (Cfg::P_TMEM) ptx::tmem_wait_st();
-            else ptx::fence_proxy_async_smem();
-            arrive_warp(p_full);
-            if (Cfg::PREFETCH && have_next) {
-                ptx::tmem_wait_ld();
+            };
+            auto max_chunk = [&](int c) {
+                float a = -INFINITY, b = -INFINITY, cc = -INFINITY, d = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) ptx::reg_fence32(&sv[c * 32]);
-                arrive_warp(s_free);           // S of tile j+1 is in registers: QK^T of tile j+2 may start
+                for (int i = 0; i < 32; i += 8) {
+                    a = ptx::max3(a, __uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1]));
+                    b = ptx::max3(b, __uint_as_float(sv[c * 32 + i + 2]), __uint_as_float(sv[c * 32 + i + 3]));
+                    cc = ptx::max3(cc, __uint_as_float(sv[c * 32 + i + 4]), __uint_as_float(sv[c * 32 + i + 5]));
+                    d = ptx::max3(d, __uint_as_float(sv[c * 32 + i + 6]), __uint_as_float(sv[c * 32 + i + 7]));
+                }
+                mx = fmaxf(mx, fmaxf(fmaxf(a, b), fmaxf(cc, d)));
+            };
+            if (ok) {
+                tick(0);
+                ok = wait_all(s_full, 0);
+                tick(SEC_SM_WAIT_S);
+                if (ok) {
+                    ptx::tc_fence_after_sync();
+                    ptx::tmem_ld_cols<BN>(t_s, sv);
+                    ptx::tmem_wait_ld();
+                    ptx::reg_fence_cols<BN>(sv);
+                    arrive_warp(s_free);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) { mask_chunk(0, c); max_chunk(c); }
+                    tick(SEC_SM_LOAD_S);
+                }
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const bool have_next = j + 1 < n_tiles;
+                const float m_new = fmaxf(m_used, mx * scale);
+                const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+                const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+                m_used = m_next;
+                mx = -INFINITY;
+                tick(SEC_SM_MAX);
+                if (j > 0) {
+                    // PV of the previous tile must be finished before P is overwritten or O rescaled
+                    ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
+                    tick(SEC_SM_WAIT_PV);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                        for (int c = 0; c < DV / 16; ++c) {
+                            uint32_t o[16];
+                            ptx::tmem_ld16(t_o + c * 16, o);
+                            ptx::tmem_wait_ld();
+                            ptx::reg_fence16(o);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            ptx::tmem_st16(t_o + c * 16, o);
+                        }
+                        ptx::tmem_wait_st();
+                    }
+                    tick(SEC_SM_RESCALE);
+                }
+                const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]),
+                                                                 __uint_as_float(sv[c * 32 + i + 1])), scale2, negm2);
+                        const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i + 2]),
+                                                                 __uint_as_float(sv[c * 32 + i + 3])), scale2, negm2);
+                        const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                        const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                        sum_a = __fadd2_rn(sum_a, ea);
+                        sum_b = __fadd2_rn(sum_b, eb);
+                        pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                        pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+                    }
+                    ptx::tmem_st16(t_p + c * 16, pk);
+                    // the registers of chunks 0..c are free: refill them with the next tile's scores
+                    if (have_next && c >= WAITC) {
+                        if (c == WAITC) {
+                            ok = wait_all(s_full, (uint32_t)(j + 1) & 1u);
+                            if (!ok) break;
+                            ptx::tc_fence_after_sync();
+#pragma unroll
+                            for (int cc = 0; cc <= WAITC; ++cc) ptx::tmem_ld32(t_s + cc * 32, &sv[cc * 32]);
+                        } else {
+                            // chunks loaded so far have landed during the exponentials above: fold them
+                            // into the next tile's maximum, then fetch one more
+                            ptx::tmem_wait_ld();
+#pragma unroll
+                            for (int cc = (c == WAITC + 1 ? 0 : c - 1); cc < c; ++cc) {
+                                ptx::reg_fence32(&sv[cc * 32]);
+                                mask_chunk(j + 1, cc);
+                                max_chunk(cc);
+                            }
+                            ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
+                        }
+                    }
+                }
+                if (!ok) break;
+                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+                tick(SEC_SM_EXP);
+                ptx::tmem_wait_st();
+                arrive_warp(p_full);
+                tick(SEC_SM_STORE_P);
+                if (have_next) {
+                    ptx::tmem_wait_ld();
+                    arrive_warp(s_free);           // S(j+1) is in registers: QK^T of tile j+2 may start
+#pragma unroll
+                    for (int cc = (NCH - 1 == WAITC ? 0 : NCH - 1); cc < NCH; ++cc) {
+                        ptx::reg_fence32(&sv[cc * 32]);
+                        mask_chunk(j + 1, cc);
+                        max_chunk(cc);
+                    }
+                    tick(SEC_SM_LOAD_S);
+                }
             }
         }
+        const long long t_loop_end = Cfg::PROF ? clock64() : 0;
         if (run && ok) {
             ok = wait_all(pv_done, (uint32_t)(n_tiles - 1) & 1u);
             if (ok) {
@@ -457,6 +639,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
         }
         if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
+        if constexpr (Cfg::PROF) {
+            if (prof_on && warp == 2 && lane == 0) {
+                p.prof[SEC_SM_TOTAL] = t_loop_end - t_begin;
+                for (int i = 1; i <= 8; ++i) p.prof[i] = prof_acc[i];
+                p.prof[SEC_SM_EPILOGUE] = clock64() - t_loop_end;
+                p.prof[SEC_SM_TILES] = n_tiles;
+            }
+        }
         if (!run && *abort_flag == 0 && row < p.Sq) {
             // no visible key at all for this tile: the reference's 0/0
             float *orow = p.out + ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
