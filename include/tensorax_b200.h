@@ -110,6 +110,18 @@ TX_API int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size);
 TX_API int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t dim_size,
                                      int64_t inner, int64_t repeats, int32_t elem_bytes);
 
+/* ---- linear layer either side of SDPA in MultiHeadAttention.forward: reference F.linear
+ *      (tensorax/functional.py:105-110) = matmul (csrc/tensor_ops.cpp:295-329, matmul_cpu
+ *      csrc/cpu/tensor_cpu.cpp:131-156) + bias, then reshape/transpose to heads
+ *      (tensorax/nn/attention/layers.py:112-128).  out = x @ W^T + bias in exact fp32;
+ *      x is [batch, seq, in_features], or [batch, heads_in, seq, in_features/heads_in] when
+ *      heads_in > 0; out is [batch, seq, out_features], or head-split
+ *      [batch, heads_out, seq, out_features/heads_out] when heads_out > 0; W is [out_features,
+ *      in_features]; bias may be NULL.  Does not synchronise. */
+TX_API int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float *out,
+                              int64_t batch, int64_t seq, int64_t in_features, int64_t out_features,
+                              int32_t heads_in, int32_t heads_out);
+
 /* ---- general form (no reference counterpart: the reference has no fp16+mask,
  *      no implicit causal / key-length mask and no grouped K/V heads; its dense
  *      mask forms cannot exist at S = 8192).  Asynchronous on `stream`. */

@@ -54,6 +54,8 @@ def _oracle():
         _lib.oracle_sdpa_structured.argtypes = (
             [_fp] * 4 + [_i64] * 7 + [ctypes.c_int, _fp] + [_i64] * 4)
         _lib.oracle_sdpa_structured.restype = None
+        _lib.oracle_linear_f32.argtypes = [_fp] * 4 + [_i64] * 3
+        _lib.oracle_linear_f32.restype = None
     return _lib
 
 
@@ -67,6 +69,8 @@ def _reference():
         _ref = ctypes.CDLL(_REF_SO)
         _ref.ref_sdpa_cpu.argtypes = [_fp] * 5 + [_i64] * 6
         _ref.ref_sdpa_cpu.restype = None
+        _ref.ref_matmul_cpu.argtypes = [_fp] * 3 + [_i64] * 4
+        _ref.ref_matmul_cpu.restype = None
     return _ref
 
 
@@ -131,3 +135,44 @@ def sdpa_structured(q, k, v, causal=False, kv_lens=None, heads=None, rows=None, 
         with ThreadPoolExecutor(max_workers=threads) as ex:
             list(ex.map(one, head_list))
     return out
+
+
+def linear_f32(x, w, bias=None):
+    """Restated F.linear: x [..., K] @ w[N, K].T + bias, reference accumulation order."""
+    x, w = _f32c(x), _f32c(w)
+    K, N = x.shape[-1], w.shape[0]
+    rows = x.size // K
+    b = None if bias is None else _f32c(bias)
+    out = np.empty(x.shape[:-1] + (N,), dtype=np.float32)
+    _oracle().oracle_linear_f32(_ptr(x), _ptr(w), _ptr(b), _ptr(out), rows, K, N)
+    return out
+
+
+def ref_linear(x, w, bias=None):
+    """F.linear through the reference's own matmul_cpu (x @ w.T, then + bias)."""
+    x, w = _f32c(x), _f32c(w)
+    K, N = x.shape[-1], w.shape[0]
+    rows = x.size // K
+    wt = np.ascontiguousarray(w.T)
+    out = np.empty(x.shape[:-1] + (N,), dtype=np.float32)
+    _reference().ref_matmul_cpu(_ptr(x), _ptr(wt), _ptr(out), 1, rows, N, K)
+    return out if bias is None else out + _f32c(bias)
+
+
+def mha_forward_f32(query, key, value, params, num_heads, mask=None):
+    """MultiHeadAttention.forward as the reference writes it (tensorax/nn/attention/layers.py:96-129),
+    composed from the restated pieces: three projections, head split, SDPA, head merge, output
+    projection.  `params` maps q/k/v/out _weight and _bias names to arrays (bias may be None)."""
+    B, Sq, E = query.shape
+    Sk = key.shape[1]
+    dh = E // num_heads
+
+    def split(t, S):
+        return np.ascontiguousarray(t.reshape(B, S, num_heads, dh).transpose(0, 2, 1, 3))
+
+    q = split(linear_f32(query, params["q_weight"], params.get("q_bias")), Sq)
+    k = split(linear_f32(key, params["k_weight"], params.get("k_bias")), Sk)
+    v = split(linear_f32(value, params["v_weight"], params.get("v_bias")), Sk)
+    a = sdpa_f32(q, k, v, mask)
+    merged = np.ascontiguousarray(a.transpose(0, 2, 1, 3)).reshape(B, Sq, E)
+    return linear_f32(merged, params["out_weight"], params.get("out_bias"))

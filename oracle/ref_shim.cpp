@@ -13,3 +13,10 @@ extern "C" __attribute__((visibility("default"))) void ref_sdpa_cpu(
 {
     tensorax::sdpa_cpu(Q, K, V, mask, out, B, H, Sq, Sk, d_k, d_v);
 }
+
+// tensorax::matmul_cpu (csrc/tensor_ops.h, csrc/cpu/tensor_cpu.cpp:131-156): a [batch, m, k] x b [batch, k, n]
+extern "C" __attribute__((visibility("default"))) void ref_matmul_cpu(
+    const float *a, const float *b, float *out, int64_t batch, int64_t m, int64_t n, int64_t k)
+{
+    tensorax::matmul_cpu(a, b, out, batch, m, n, k);
+}

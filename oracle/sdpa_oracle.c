@@ -133,3 +133,20 @@ ORACLE_API void oracle_sdpa_structured(const float *Q, const float *K, const flo
     free(attn);
     free(mrow);
 }
+
+/*
+ * Linear layer of the reference: F.linear (tensorax/functional.py:105-110) is
+ * `x @ weight.T` through matmul_cpu (csrc/cpu/tensor_cpu.cpp:131-156: the output
+ * element starts at 0.0f and accumulates a[i,p]*b[p,j] for p ascending) followed by
+ * a broadcast add of the bias.  x [rows, K], w [N, K], bias [N] or NULL, out [rows, N].
+ */
+ORACLE_API void oracle_linear_f32(const float *x, const float *w, const float *bias, float *out,
+                                  int64_t rows, int64_t K, int64_t N)
+{
+    for (int64_t i = 0; i < rows; ++i)
+        for (int64_t j = 0; j < N; ++j) {
+            float acc = 0.0f;
+            for (int64_t p = 0; p < K; ++p) acc += x[i * K + p] * w[j * K + p];
+            out[i * N + j] = bias ? acc + bias[j] : acc;
+        }
+}

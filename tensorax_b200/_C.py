@@ -159,6 +159,44 @@ def cast_to_fp16(src: TensorImpl) -> TensorImpl:
     return dst
 
 
+def linear(x: TensorImpl, weight: TensorImpl, bias: Optional[TensorImpl] = None, heads_in: int = 0,
+           heads_out: int = 0) -> TensorImpl:
+    """x @ weight.T + bias on CUDA, exact fp32 (reference: F.linear -> matmul,
+    tensorax/functional.py:105-110, csrc/tensor_ops.cpp:295-329).  No reference counterpart for
+    `heads_in` / `heads_out`: they fold MultiHeadAttention's reshape + transpose(1, 2)
+    (tensorax/nn/attention/layers.py:117-125) into the projection -- x read as
+    [B, heads_in, S, K/heads_in], result written as [B, heads_out, S, N/heads_out]."""
+    if x.device != "cuda" or weight.device != "cuda" or (bias is not None and bias.device != "cuda"):
+        raise RuntimeError("linear: tensorax_b200 implements the CUDA path only")
+    if x.dtype != "float32" or weight.dtype != "float32":
+        raise RuntimeError("linear: float32 tensors expected")
+    if len(weight._shape) != 2:
+        raise RuntimeError("linear: weight must be [out_features, in_features]")
+    N, K = weight._shape
+    if heads_in:
+        if len(x._shape) != 4 or x._shape[1] != heads_in or x._shape[1] * x._shape[3] != K:
+            raise RuntimeError("linear: head-split input must be [B, heads, S, in_features/heads]")
+        B, S = x._shape[0], x._shape[2]
+    else:
+        if x._shape[-1] != K or len(x._shape) not in (2, 3):
+            raise RuntimeError("linear: input must be [S, in_features] or [B, S, in_features]")
+        B, S = (1, x._shape[0]) if len(x._shape) == 2 else (x._shape[0], x._shape[1])
+    if bias is not None and list(bias._shape) != [N]:
+        raise RuntimeError("linear: bias must be [out_features]")
+    if heads_out:
+        if N % heads_out:
+            raise RuntimeError("linear: out_features must be a multiple of heads_out")
+        out_shape = [B, heads_out, S, N // heads_out]
+    else:
+        out_shape = [S, N] if (len(x._shape) == 2 and not heads_in) else [B, S, N]
+    out = TensorImpl(out_shape, "float32", "cuda")
+    lib = _lib.load()
+    _lib.check(lib.tx_linear_f32_cuda(x.data_ptr, weight.data_ptr, bias.data_ptr if bias is not None else None,
+                                      out.data_ptr, B, S, K, N, int(heads_in), int(heads_out)))
+    _lib.check(lib.tx_cuda_synchronize())
+    return out
+
+
 # ------------------------------------------------------------------ SDPA dispatchers
 def _validate(query, key, value, mask, who="SDPA"):
     """Validation order and messages of csrc/tensor_ops.cpp:855-898."""

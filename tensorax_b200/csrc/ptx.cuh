@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the attention
-// kernels use: mbarrier, TMA tile loads (never with cluster multicast), tensor
+// kernels use: mbarrier, TMA tile loads (each CTA fetches its own tiles), tensor
 // memory allocation, tcgen05 MMA / commit / ld / st and the proxy fences.
 // Every wait is bounded: a wait that runs out returns false so that the caller
 // can record an error code and leave instead of spinning for ever.
@@ -100,7 +100,7 @@ __device__ __forceinline__ void tc_fence_after_sync()
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// ---------------------------------------------------------------- TMA (no multicast)
+// ---------------------------------------------------------------- TMA (per-CTA loads only)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

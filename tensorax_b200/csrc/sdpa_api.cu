@@ -15,7 +15,9 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
+#include "linear_simt.cuh"
 #include "sdpa_simt.cuh"
 #include "sdpa_tc.cuh"
 
@@ -201,17 +203,11 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
-    const int tune = (d->flags >> 3) & 7;     // tuning switch while the pipelined loop is characterised
     switch (d->d_k) {
     case 64:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 3>>(d, st, status);
-        if (tune == 2) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 2>>(d, st, status);
-        if (tune == 4) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 4>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
     case 128:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 1>>(d, st, status);
-        if (tune == 2) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 2>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:
@@ -328,6 +324,36 @@ int workspace(size_t bytes, void **out)
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Streams and events of the host-buffer form, created once per device.
+constexpr int kHostChunks = 8;
+struct HostPipe {
+    bool ready = false;
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, out_done = nullptr, in_done[kHostChunks] = {}, k_done[kHostChunks] = {};
+};
+HostPipe g_pipe[kMaxDevices];
+
+int host_pipe(HostPipe **out)
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(TX_ERR_INVALID, "device index %d out of range", dev);
+    HostPipe &p = g_pipe[dev];
+    if (!p.ready) {
+        TX_CUDA(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking));
+        TX_CUDA(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking));
+        TX_CUDA(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming));
+        TX_CUDA(cudaEventCreateWithFlags(&p.out_done, cudaEventDisableTiming));
+        for (int i = 0; i < kHostChunks; ++i) {
+            TX_CUDA(cudaEventCreateWithFlags(&p.in_done[i], cudaEventDisableTiming));
+            TX_CUDA(cudaEventCreateWithFlags(&p.k_done[i], cudaEventDisableTiming));
+        }
+        p.ready = true;
+    }
+    *out = &p;
+    return TX_OK;
+}
 
 // ------------------------------------------------------------------ allocation-free form
 // Scratch of tx_sdpa_fp16_static_scratch: [0,256) status word (+ padding), then up to
@@ -526,6 +552,28 @@ int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t 
     return TX_OK;
 }
 
+int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float *out, int64_t batch,
+                       int64_t seq, int64_t in_features, int64_t out_features, int32_t heads_in,
+                       int32_t heads_out)
+{
+    if (!x || !w || !out || batch <= 0 || seq <= 0 || in_features <= 0 || out_features <= 0)
+        return fail(TX_ERR_INVALID, "linear: bad arguments");
+    if (heads_in < 0 || heads_out < 0 || (heads_in > 0 && in_features % heads_in) ||
+        (heads_out > 0 && out_features % heads_out))
+        return fail(TX_ERR_INVALID, "linear: feature count must be a multiple of the head count");
+    if (int rc = ensure_device()) return rc;
+    txb::LinearParams p;
+    p.x = x; p.w = w; p.bias = bias; p.out = out;
+    p.B = batch; p.S = seq; p.K = in_features; p.N = out_features;
+    p.heads_in = heads_in; p.heads_out = heads_out;
+    const int64_t gy = (batch * seq + txb::LIN_BM - 1) / txb::LIN_BM, gx = (out_features + txb::LIN_BN - 1) / txb::LIN_BN;
+    if (gy > 65535 || gx > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "linear: too many rows for one launch");
+    txb::linear_simt_kernel<<<dim3((unsigned)gx, (unsigned)gy), txb::LIN_THREADS>>>(p);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
 int tx_sdpa_forward(const tx_sdpa_desc *desc) { return forward(desc); }
 
 int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
@@ -543,13 +591,8 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     int rc = TX_OK;
     if (cudaMemsetAsync(dev, 0, 32 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
     if (rc == TX_OK) {
-        const int tune = (d->flags >> 3) & 7;
-        if (d->d_k == 64)
-            rc = tune == 1 ? launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, 3>>(d, st, status, dev)
-                           : launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status, dev);
-        else
-            rc = tune == 1 ? launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true, 1>>(d, st, status, dev)
-                           : launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
+        if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status, dev);
+        else rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
     }
     if (rc == TX_OK) rc = finish(st);
     if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
@@ -573,30 +616,61 @@ int tx_sdpa_forward_host(const tx_sdpa_desc *h)
     if (int rc = validate(h)) return rc;
     if (h->mask) return fail(TX_ERR_UNSUPPORTED, "SDPA host form: dense masks are not taken; use causal / kv_lens");
     if (int rc = ensure_device()) return rc;
+    // The call is cut into chunks of whole (batch, K/V head) units -- contiguous slabs of Q, K, V and
+    // O -- so that the upload of chunk i+1, the kernel of chunk i and the download of chunk i-1 run
+    // at the same time on three streams (PCIe is full duplex; with pinned host buffers the copies
+    // are asynchronous).
+    const int64_t units = h->batch * h->kv_heads, group = h->q_heads / h->kv_heads;
     const size_t es = h->dtype == TX_DTYPE_F16 ? 2 : 4;
-    const size_t nq = (size_t)(h->batch * h->q_heads * h->seq_q * h->d_k) * es;
-    const size_t nk = (size_t)(h->batch * h->kv_heads * h->seq_k * h->d_k) * es;
-    const size_t nv = (size_t)(h->batch * h->kv_heads * h->seq_k * h->d_v) * es;
-    const size_t no = (size_t)(h->batch * h->q_heads * h->seq_q * h->d_v) * 4;
-    const size_t nl = h->kv_lens ? (size_t)h->batch * 4 : 0;
-    const size_t oq = 0, ok = align_up(oq + nq, 256), ov = align_up(ok + nk, 256),
-                 oo = align_up(ov + nv, 256), ol = align_up(oo + no, 256);
+    const size_t uq = (size_t)(group * h->seq_q * h->d_k) * es;       // bytes of one unit
+    const size_t uk = (size_t)(h->seq_k * h->d_k) * es;
+    const size_t uv = (size_t)(h->seq_k * h->d_v) * es;
+    const size_t uo = (size_t)(group * h->seq_q * h->d_v) * 4;
+    const size_t nl = h->kv_lens ? (size_t)units * 4 : 0;
+    const size_t oq = 0, ok = align_up(oq + uq * units, 256), ov = align_up(ok + uk * units, 256),
+                 oo = align_up(ov + uv * units, 256), ol = align_up(oo + uo * units, 256);
     const size_t total = align_up(ol + nl, 256);
     std::lock_guard<std::mutex> lk(g_ws_mu);
     void *base = nullptr;
     if (int rc = workspace(total, &base)) return rc;
     char *w = static_cast<char *>(base);
+    HostPipe *hp = nullptr;
+    if (int rc = host_pipe(&hp)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(h->stream);
-    TX_CUDA(cudaMemcpyAsync(w + oq, h->q, nq, cudaMemcpyHostToDevice, st));
-    TX_CUDA(cudaMemcpyAsync(w + ok, h->k, nk, cudaMemcpyHostToDevice, st));
-    TX_CUDA(cudaMemcpyAsync(w + ov, h->v, nv, cudaMemcpyHostToDevice, st));
-    if (nl) TX_CUDA(cudaMemcpyAsync(w + ol, h->kv_lens, nl, cudaMemcpyHostToDevice, st));
-    tx_sdpa_desc d = *h;
-    d.q = w + oq; d.k = w + ok; d.v = w + ov;
-    d.out = reinterpret_cast<float *>(w + oo);
-    d.kv_lens = nl ? reinterpret_cast<const int32_t *>(w + ol) : nullptr;
-    if (int rc = forward(&d)) return rc;
-    TX_CUDA(cudaMemcpyAsync(h->out, w + oo, no, cudaMemcpyDeviceToHost, st));
+
+    int n_chunks = (int)std::min<int64_t>(units, kHostChunks);
+    const size_t bytes_total = (uq + uk + uv + uo) * (size_t)units;
+    if (bytes_total < (8u << 20)) n_chunks = 1;                          // too small to be worth cutting
+    // everything below is ordered after what the caller already put on its stream
+    TX_CUDA(cudaEventRecord(hp->start, st));
+    TX_CUDA(cudaStreamWaitEvent(hp->in, hp->start, 0));
+    TX_CUDA(cudaStreamWaitEvent(hp->out, hp->start, 0));
+    std::vector<int32_t> unit_lens;
+    if (nl) {
+        unit_lens.resize((size_t)units);
+        for (int64_t u = 0; u < units; ++u) unit_lens[(size_t)u] = h->kv_lens[u / h->kv_heads];
+        TX_CUDA(cudaMemcpyAsync(w + ol, unit_lens.data(), nl, cudaMemcpyHostToDevice, hp->in));
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+        const int64_t u0 = units * c / n_chunks, u1 = units * (c + 1) / n_chunks, nu = u1 - u0;
+        if (nu <= 0) continue;
+        TX_CUDA(cudaMemcpyAsync(w + oq + uq * u0, static_cast<const char *>(h->q) + uq * u0, uq * nu, cudaMemcpyHostToDevice, hp->in));
+        TX_CUDA(cudaMemcpyAsync(w + ok + uk * u0, static_cast<const char *>(h->k) + uk * u0, uk * nu, cudaMemcpyHostToDevice, hp->in));
+        TX_CUDA(cudaMemcpyAsync(w + ov + uv * u0, static_cast<const char *>(h->v) + uv * u0, uv * nu, cudaMemcpyHostToDevice, hp->in));
+        TX_CUDA(cudaEventRecord(hp->in_done[c], hp->in));
+        TX_CUDA(cudaStreamWaitEvent(st, hp->in_done[c], 0));
+        tx_sdpa_desc d = *h;                       // the chunk as a problem of its own: one K/V head per "batch"
+        d.q = w + oq + uq * u0; d.k = w + ok + uk * u0; d.v = w + ov + uv * u0;
+        d.out = reinterpret_cast<float *>(w + oo + uo * u0);
+        d.kv_lens = nl ? reinterpret_cast<const int32_t *>(w + ol) + u0 : nullptr;
+        d.batch = nu; d.q_heads = group; d.kv_heads = 1;
+        if (int rc = forward(&d)) return rc;
+        TX_CUDA(cudaEventRecord(hp->k_done[c], st));
+        TX_CUDA(cudaStreamWaitEvent(hp->out, hp->k_done[c], 0));
+        TX_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(h->out) + uo * u0, w + oo + uo * u0, uo * nu, cudaMemcpyDeviceToHost, hp->out));
+    }
+    TX_CUDA(cudaEventRecord(hp->out_done, hp->out));
+    TX_CUDA(cudaStreamWaitEvent(st, hp->out_done, 0));      // the caller's stream ends after the last download
     return finish(st);
 }
 

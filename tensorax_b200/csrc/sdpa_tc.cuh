@@ -70,13 +70,9 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int PIPE_ = 0>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false>
 struct TcCfg {
     static constexpr bool PROF = PROF_;   // collect the section profile
-    // PIPE > 0: the softmax loop refills the registers of finished 32-column chunks with the next
-    // tile's scores while the remaining chunks are exponentiated; the next tile's S is awaited after
-    // chunk PIPE-1.  PIPE = 0: load, max, exponentiate, store, one after the other.
-    static constexpr int PIPE = PIPE_;
     static constexpr int DK = DK_;        // head dim of Q and K
     static constexpr int DV = DV_;        // value columns this CTA owns
     static constexpr int BN = BN_;        // keys per tile
@@ -112,7 +108,6 @@ struct TcCfg {
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
     static_assert(DK % 64 == 0 && DV % 64 == 0, "panels are 64 columns wide");
     static_assert(BN % 32 == 0 && (P_TMEM || BN % 64 == 0), "P in shared memory needs 64-column panels");
-    static_assert(PIPE == 0 || (P_TMEM && PIPE <= BN / 32), "the pipelined loop stores P to tensor memory chunk by chunk");
     static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
     static_assert(BN <= 256 && DV <= 256, "one MMA instruction covers N <= 256");
     static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA may have");
@@ -362,14 +357,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
         float l = 0.f;
         bool ok = run;
-        // One lane polls; the warp then converges, so the .sync.aligned tensor-memory
-        // instructions that follow are always executed by the whole warp.
+        // Every lane polls the same barrier with the same instruction, so the answer is the same
+        // for the whole warp and the .sync.aligned tensor-memory instructions that follow are
+        // executed by all of it (polling from one lane and broadcasting cost more than it saved).
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
-            int done = 1;
-            if (lane == 0) done = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-            done = __shfl_sync(0xffffffffu, done, 0);
-            __syncwarp();
-            return done != 0;
+            return ptx::mbar_wait(bar, parity, abort_flag);
         };
         // Every lane has fenced its own tensor-memory / shared-memory writes; one lane
         // then arrives for the warp.
@@ -380,236 +372,101 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         };
         tick_start();
         const long long t_begin = Cfg::PROF ? clock64() : 0;
-        if constexpr (Cfg::PIPE == 0) {
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int kv0 = j * BN;
-                tick(0);
-                ok = wait_all(s_full, (uint32_t)j & 1u);
-                tick(SEC_SM_WAIT_S);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int kv0 = j * BN;
+            tick(0);
+            ok = wait_all(s_full, (uint32_t)j & 1u);
+            tick(SEC_SM_WAIT_S);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            // this thread's part of the S row in registers, one wait; then S belongs to the MMA warp again
+            uint32_t sv[BN];
+            ptx::tmem_ld_cols<BN>(t_s, sv);
+            ptx::tmem_wait_ld();
+            ptx::reg_fence_cols<BN>(sv);
+            arrive_warp(s_free);
+            tick(SEC_SM_LOAD_S);
+
+            const bool need_mask = (j * BN + BN > kv_limit) || (p.causal && (j * BN + BN - 1 > q0));
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int col = kv0 + i;
+                    const bool vis = col < kv_limit && (!p.causal || col <= row);
+                    if (!vis) sv[i] = 0xff800000u;       // -inf
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN; i += 8) {
+                mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            tick(SEC_SM_MAX);
+            const float m_new = fmaxf(m_used, mx * scale);
+            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+            m_used = m_next;
+            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+            const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+            uint32_t pk[BN / 2];
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
+                                             scale2, negm2);
+                const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
+                                             scale2, negm2);
+                const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                sum_a = __fadd2_rn(sum_a, ea);
+                sum_b = __fadd2_rn(sum_b, eb);
+                pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+            }
+            l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+            tick(SEC_SM_EXP);
+            if (j > 0) {
+                // PV of the previous tile must be finished before P is overwritten or O rescaled
+                ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
+                tick(SEC_SM_WAIT_PV);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                // this thread's part of the S row in registers, one wait; then S belongs to the MMA warp again
-                uint32_t sv[BN];
-                ptx::tmem_ld_cols<BN>(t_s, sv);
-                ptx::tmem_wait_ld();
-                ptx::reg_fence_cols<BN>(sv);
-                arrive_warp(s_free);
-                tick(SEC_SM_LOAD_S);
-
-                const bool need_mask = (j * BN + BN > kv_limit) || (p.causal && (j * BN + BN - 1 > q0));
-                if (need_mask) {
-    #pragma unroll
-                    for (int i = 0; i < BN; ++i) {
-                        const int col = kv0 + i;
-                        const bool vis = col < kv_limit && (!p.causal || col <= row);
-                        if (!vis) sv[i] = 0xff800000u;       // -inf
-                    }
-                }
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-    #pragma unroll
-                for (int i = 0; i < BN; i += 8) {
-                    mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-                    mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
-                    mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
-                    mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
-                }
-                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-                tick(SEC_SM_MAX);
-                const float m_new = fmaxf(m_used, mx * scale);
-                const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
-                const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
-                m_used = m_next;
-                // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
-                const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
-                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-                uint32_t pk[BN / 2];
-    #pragma unroll
-                for (int i = 0; i < BN; i += 4) {
-                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
-                                                 scale2, negm2);
-                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
-                                                 scale2, negm2);
-                    const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
-                    const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
-                    sum_a = __fadd2_rn(sum_a, ea);
-                    sum_b = __fadd2_rn(sum_b, eb);
-                    pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
-                    pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
-                }
-                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
-                tick(SEC_SM_EXP);
-                if (j > 0) {
-                    // PV of the previous tile must be finished before P is overwritten or O rescaled
-                    ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
-                    tick(SEC_SM_WAIT_PV);
-                    if (!ok) break;
-                    ptx::tc_fence_after_sync();
-                    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                        // rare after the first tiles; 16 columns at a time so the score row stays in registers
-    #pragma unroll 1
-                        for (int c = 0; c < DV / 16; ++c) {
-                            uint32_t o[16];
-                            ptx::tmem_ld16(t_o + c * 16, o);
-                            ptx::tmem_wait_ld();
-                            ptx::reg_fence16(o);
-    #pragma unroll
-                            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            ptx::tmem_st16(t_o + c * 16, o);
-                        }
-                        ptx::tmem_wait_st();
-                    }
-                    tick(SEC_SM_RESCALE);
-                }
-                if constexpr (Cfg::P_TMEM) {
-                    ptx::tmem_st_cols<BN / 2>(t_p, pk);
-                    ptx::tmem_wait_st();
-                } else {
-                    // row r of P: 64-column panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
-    #pragma unroll
-                    for (int q = 0; q < BN / 8; ++q) {
-                        const int ch = q;
-                        const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
-                                              (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
-                        ptx::st_shared_v4(addr, pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
-                    }
-                    ptx::fence_proxy_async_smem();
-                }
-                arrive_warp(p_full);
-                tick(SEC_SM_STORE_P);
-            }
-        } else {
-            // ---- pipelined form.  Invariant at the top of iteration j: sv holds row r of S(j), masked,
-            // and mx is its maximum; S in tensor memory already belongs to the MMA warp again.
-            constexpr int NCH = BN / 32;
-            constexpr int WAITC = Cfg::PIPE - 1;
-            uint32_t sv[BN];
-            float mx = -INFINITY;
-            auto mask_chunk = [&](int j_tile, int c) {
-                const int kv0 = j_tile * BN;
-                const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
-                if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = kv0 + c * 32 + i;
-                        const bool vis = col < kv_limit && (!p.causal || col <= row);
-                        if (!vis) sv[c * 32 + i] = 0xff800000u;       // -inf
-                    }
-                }
-            };
-            auto max_chunk = [&](int c) {
-                float a = -INFINITY, b = -INFINITY, cc = -INFINITY, d = -INFINITY;
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    a = ptx::max3(a, __uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1]));
-                    b = ptx::max3(b, __uint_as_float(sv[c * 32 + i + 2]), __uint_as_float(sv[c * 32 + i + 3]));
-                    cc = ptx::max3(cc, __uint_as_float(sv[c * 32 + i + 4]), __uint_as_float(sv[c * 32 + i + 5]));
-                    d = ptx::max3(d, __uint_as_float(sv[c * 32 + i + 6]), __uint_as_float(sv[c * 32 + i + 7]));
-                }
-                mx = fmaxf(mx, fmaxf(fmaxf(a, b), fmaxf(cc, d)));
-            };
-            if (ok) {
-                tick(0);
-                ok = wait_all(s_full, 0);
-                tick(SEC_SM_WAIT_S);
-                if (ok) {
-                    ptx::tc_fence_after_sync();
-                    ptx::tmem_ld_cols<BN>(t_s, sv);
-                    ptx::tmem_wait_ld();
-                    ptx::reg_fence_cols<BN>(sv);
-                    arrive_warp(s_free);
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c) { mask_chunk(0, c); max_chunk(c); }
-                    tick(SEC_SM_LOAD_S);
-                }
-            }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const bool have_next = j + 1 < n_tiles;
-                const float m_new = fmaxf(m_used, mx * scale);
-                const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
-                const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
-                m_used = m_next;
-                mx = -INFINITY;
-                tick(SEC_SM_MAX);
-                if (j > 0) {
-                    // PV of the previous tile must be finished before P is overwritten or O rescaled
-                    ok = wait_all(pv_done, (uint32_t)(j - 1) & 1u);
-                    tick(SEC_SM_WAIT_PV);
-                    if (!ok) break;
-                    ptx::tc_fence_after_sync();
-                    if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    // rare after the first tiles; 16 columns at a time so the score row stays in registers
 #pragma unroll 1
-                        for (int c = 0; c < DV / 16; ++c) {
-                            uint32_t o[16];
-                            ptx::tmem_ld16(t_o + c * 16, o);
-                            ptx::tmem_wait_ld();
-                            ptx::reg_fence16(o);
+                    for (int c = 0; c < DV / 16; ++c) {
+                        uint32_t o[16];
+                        ptx::tmem_ld16(t_o + c * 16, o);
+                        ptx::tmem_wait_ld();
+                        ptx::reg_fence16(o);
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            ptx::tmem_st16(t_o + c * 16, o);
-                        }
-                        ptx::tmem_wait_st();
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st16(t_o + c * 16, o);
                     }
-                    tick(SEC_SM_RESCALE);
+                    ptx::tmem_wait_st();
                 }
-                const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
-                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i]),
-                                                                 __uint_as_float(sv[c * 32 + i + 1])), scale2, negm2);
-                        const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c * 32 + i + 2]),
-                                                                 __uint_as_float(sv[c * 32 + i + 3])), scale2, negm2);
-                        const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
-                        const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
-                        sum_a = __fadd2_rn(sum_a, ea);
-                        sum_b = __fadd2_rn(sum_b, eb);
-                        pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
-                        pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
-                    }
-                    ptx::tmem_st16(t_p + c * 16, pk);
-                    // the registers of chunks 0..c are free: refill them with the next tile's scores
-                    if (have_next && c >= WAITC) {
-                        if (c == WAITC) {
-                            ok = wait_all(s_full, (uint32_t)(j + 1) & 1u);
-                            if (!ok) break;
-                            ptx::tc_fence_after_sync();
-#pragma unroll
-                            for (int cc = 0; cc <= WAITC; ++cc) ptx::tmem_ld32(t_s + cc * 32, &sv[cc * 32]);
-                        } else {
-                            // chunks loaded so far have landed during the exponentials above: fold them
-                            // into the next tile's maximum, then fetch one more
-                            ptx::tmem_wait_ld();
-#pragma unroll
-                            for (int cc = (c == WAITC + 1 ? 0 : c - 1); cc < c; ++cc) {
-                                ptx::reg_fence32(&sv[cc * 32]);
-                                mask_chunk(j + 1, cc);
-                                max_chunk(cc);
-                            }
-                            ptx::tmem_ld32(t_s + c * 32, &sv[c * 32]);
-                        }
-                    }
-                }
-                if (!ok) break;
-                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
-                tick(SEC_SM_EXP);
-                ptx::tmem_wait_st();
-                arrive_warp(p_full);
-                tick(SEC_SM_STORE_P);
-                if (have_next) {
-                    ptx::tmem_wait_ld();
-                    arrive_warp(s_free);           // S(j+1) is in registers: QK^T of tile j+2 may start
-#pragma unroll
-                    for (int cc = (NCH - 1 == WAITC ? 0 : NCH - 1); cc < NCH; ++cc) {
-                        ptx::reg_fence32(&sv[cc * 32]);
-                        mask_chunk(j + 1, cc);
-                        max_chunk(cc);
-                    }
-                    tick(SEC_SM_LOAD_S);
-                }
+                tick(SEC_SM_RESCALE);
             }
+            if constexpr (Cfg::P_TMEM) {
+                ptx::tmem_st_cols<BN / 2>(t_p, pk);
+                ptx::tmem_wait_st();
+            } else {
+                // row r of P: 64-column panels, each row 128 bytes = 8 chunks of 8 halves, chunk ^= r%8
+#pragma unroll
+                for (int q = 0; q < BN / 8; ++q) {
+                    const int ch = q;
+                    const uint32_t addr = p_s + (ch >> 3) * (BM * 128) + r * 128 +
+                                          (((uint32_t)(ch & 7) ^ (uint32_t)(r & 7)) << 4);
+                    ptx::st_shared_v4(addr, pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+                }
+                ptx::fence_proxy_async_smem();
+            }
+            arrive_warp(p_full);
+            tick(SEC_SM_STORE_P);
         }
         const long long t_loop_end = Cfg::PROF ? clock64() : 0;
         if (run && ok) {

@@ -25,6 +25,13 @@ def _result(c_tensor, requires_grad=False, grad_fn=None) -> Tensor:
     return out
 
 
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None) -> Tensor:
+    """Linear transformation x @ weight.T + bias (tensorax/functional.py:105-110), CUDA tensors."""
+    if not _C:
+        raise RuntimeError("C++ backend not available.")
+    return _result(_C.linear(x._c_tensor, weight._c_tensor, bias._c_tensor if bias is not None else None))
+
+
 def _check(query, key, value, mask, msg4d):
     if len(query.shape) != 4 or len(key.shape) != 4 or len(value.shape) != 4:
         raise ValueError(msg4d)

@@ -62,16 +62,19 @@ class GroupedQueryAttention:
 
 class MultiHeadAttention:
     """Multi-head attention (layers.py:53-135): same constructor, parameters,
-    initialisation scale and ``repr``.
+    initialisation scale, ``forward`` signature and ``repr``.
 
-    The reference's ``forward`` cannot run (it calls the unbound
-    ``_C.transpose_dims``, tensorax/tensor.py:976).  The attention it would issue
-    is the SDPA call on [batch, num_heads, seq, head_dim] (layers.py:122);
-    ``attend`` runs exactly that call.  The four projections are GEMMs outside
-    this package's scope, so ``forward`` raises until they are built.
+    ``forward`` does what the reference's forward spells out -- three projections,
+    split into heads, SDPA, merge, output projection (layers.py:112-128) -- on CUDA
+    tensors.  The reference cannot run its own forward (it calls the unbound
+    ``_C.transpose_dims``, tensorax/tensor.py:976); here the reshape + transpose
+    steps are folded into the projections, which write and read the
+    [batch, heads, seq, head_dim] layout directly.  ``dropout`` is stored and never
+    applied, as in the reference.
     """
 
-    def __init__(self, embed_dim: int, num_heads: int, bias: bool = True, dropout: float = 0.0):
+    def __init__(self, embed_dim: int, num_heads: int, bias: bool = True, dropout: float = 0.0,
+                 device: str = "cpu"):
         if embed_dim % num_heads != 0:
             raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads})")
         self.embed_dim = embed_dim
@@ -83,12 +86,19 @@ class MultiHeadAttention:
         rng = np.random.default_rng()
         for name in ("q_weight", "k_weight", "v_weight", "out_weight"):
             w = (rng.standard_normal((embed_dim, embed_dim)) * std).astype(np.float32)
-            self._parameters[name] = Tensor(w, requires_grad=True)
+            self._parameters[name] = Tensor(w, device=device, requires_grad=True)
         for name in ("q_bias", "k_bias", "v_bias", "out_bias"):
-            self._parameters[name] = Tensor.zeros((embed_dim,), requires_grad=True) if bias else None
+            self._parameters[name] = (Tensor.zeros((embed_dim,), device=device, requires_grad=True)
+                                      if bias else None)
 
     def parameters(self):
         return [p for p in self._parameters.values() if p is not None]
+
+    def cuda(self) -> "MultiHeadAttention":
+        for name, p in self._parameters.items():
+            if p is not None:
+                self._parameters[name] = p.cuda()
+        return self
 
     def attend(self, q: Tensor, k: Tensor, v: Tensor, mask: Tensor = None, causal: bool = False,
                kv_lens=None) -> Tensor:
@@ -101,9 +111,24 @@ class MultiHeadAttention:
         return F.scaled_dot_product_attention(q, k, v, mask)
 
     def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
-        raise NotImplementedError(
-            "MultiHeadAttention.forward needs the Q/K/V/output projection GEMMs, which are outside "
-            "the SDPA forward path this package implements; project and split heads, then call attend()")
+        """query (batch, seq_q, embed_dim); key, value (batch, seq_k, embed_dim); mask optional
+        (batch, num_heads, seq_q, seq_k).  Returns (batch, seq_q, embed_dim)."""
+        from ... import _C
+        P = self._parameters
+
+        def project(x, w, b):
+            return Tensor._wrap(_C.linear(x._c_tensor, P[w]._c_tensor,
+                                          P[b]._c_tensor if P[b] is not None else None,
+                                          heads_out=self.num_heads))
+
+        q = project(query, "q_weight", "q_bias")          # (batch, heads, seq, head_dim), no transpose pass
+        k = project(key, "k_weight", "k_bias")
+        v = project(value, "v_weight", "v_bias")
+        attn = F.scaled_dot_product_attention(q, k, v, mask)
+        out = _C.linear(attn._c_tensor, P["out_weight"]._c_tensor,
+                        P["out_bias"]._c_tensor if P["out_bias"] is not None else None,
+                        heads_in=self.num_heads)         # heads merged while reading
+        return Tensor._wrap(out)
 
     def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
         return self.forward(query, key, value, mask)

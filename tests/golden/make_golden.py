@@ -22,6 +22,9 @@ Cases
   gqa_*         grouped K/V heads + causal + key lengths, expressed the only way the
                 reference can: K/V replicated head-wise (repeat_interleave semantics,
                 csrc/tensor_ops.cpp:145-154) and a dense 0/-inf mask
+  lin_*, mha_*  F.linear (tensorax/functional.py:105-110) through the reference's matmul_cpu, and
+                MultiHeadAttention.forward (tensorax/nn/attention/layers.py:112-128) composed from the
+                reference's matmul_cpu + sdpa_cpu (the reference cannot run that forward itself)
 Large outputs are stored as sampled rows (`*_rows` gives the row indices).
 """
 from __future__ import annotations
@@ -117,6 +120,26 @@ def main():
     mask = np.broadcast_to(np.where(vis, 0.0, -np.inf).astype(np.float32), (B, Hq, S, S)).copy()
     g.update(gqa_q=q.astype(np.float16), gqa_k=k.astype(np.float16), gqa_v=v.astype(np.float16),
              gqa_lens=lens, gqa_out=ref(q, krep, vrep, mask))
+
+    # ---- the linear layers either side of SDPA in MultiHeadAttention.forward, and the whole forward,
+    #      composed from the reference's own matmul_cpu and sdpa_cpu exactly as layers.py:112-128 spells out
+    x, w, b = seeded(601, 2, 9, 24), seeded(602, 10, 24), seeded(603, 10)
+    g.update(lin_x=x, lin_w=w, lin_b=b, lin_out=oracle.ref_linear(x, w, b), lin_out_nobias=oracle.ref_linear(x, w))
+    B, S, Sk, E, H = 2, 10, 13, 32, 4
+    xq, xk, xv = seeded(611, B, S, E), seeded(612, B, Sk, E), seeded(613, B, Sk, E)
+    std = np.float32(np.sqrt(2.0 / (E + E)))
+    P = {n: seeded(620 + i, E, E) * std for i, n in enumerate(("q_weight", "k_weight", "v_weight", "out_weight"))}
+    P.update({n: 0.1 * seeded(630 + i, E) for i, n in enumerate(("q_bias", "k_bias", "v_bias", "out_bias"))})
+
+    def split(t, S_):
+        return np.ascontiguousarray(t.reshape(B, S_, H, E // H).transpose(0, 2, 1, 3))
+
+    q = split(oracle.ref_linear(xq, P["q_weight"], P["q_bias"]), S)
+    k = split(oracle.ref_linear(xk, P["k_weight"], P["k_bias"]), Sk)
+    v = split(oracle.ref_linear(xv, P["v_weight"], P["v_bias"]), Sk)
+    a = np.ascontiguousarray(ref(q, k, v).transpose(0, 2, 1, 3)).reshape(B, S, E)
+    g.update(mha_xq=xq, mha_xk=xk, mha_xv=xv, mha_out=oracle.ref_linear(a, P["out_weight"], P["out_bias"]),
+             **{f"mha_{n}": arr for n, arr in P.items()})
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "sdpa_golden.npz")
     np.savez_compressed(path, **g)

@@ -104,3 +104,13 @@ def test_restatement_equals_reference_library():
         m[m > 1.2] = -np.inf
         assert bit_equal(oracle.sdpa_f32(q, k, v), oracle.ref_sdpa_cpu(q, k, v))
         assert bit_equal(oracle.sdpa_f32(q, k, v, m), oracle.ref_sdpa_cpu(q, k, v, m))
+
+
+def test_linear_and_mha_forward_restatements(golden):
+    x, w, b = golden["lin_x"], golden["lin_w"], golden["lin_b"]
+    assert bit_equal(oracle.linear_f32(x, w, b), golden["lin_out"])
+    assert bit_equal(oracle.linear_f32(x, w), golden["lin_out_nobias"])
+    params = {n: golden[f"mha_{n}"] for n in ("q_weight", "k_weight", "v_weight", "out_weight",
+                                               "q_bias", "k_bias", "v_bias", "out_bias")}
+    out = oracle.mha_forward_f32(golden["mha_xq"], golden["mha_xk"], golden["mha_xv"], params, num_heads=4)
+    assert bit_equal(out, golden["mha_out"])
