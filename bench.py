@@ -46,9 +46,9 @@ FLOPS_PER_STEP = 4.0 * B * H * S * S * D                    # 549.76 GFLOP, per 
 ALG_BYTES_PER_STEP = B * H * S * D * (2 + 2 + 2 + 4)        # Q,K,V fp16 reads + O fp32 write
 METRIC = "fp16 SDPA fwd TFLOP/s per GPU at B4 H8 S8192 d64; % of B200 dense fp16 peak"
 PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070 Ti Laptop (sm_86)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists)
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel: mean of the two
+# launches captured with `ncu --set full` (profiles/sdpa_tc_kernel_config2_d64.md: 135.87 MB, 137.68 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 136_770_000
 WORKLOAD = "config2: SDPA fwd fp16 (fp32 accumulate) B=4 H=8 S=8192 d=64 non-causal, no mask"
 
 
@@ -93,7 +93,7 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-def run_reference_arm(args, rank, world):
+def run_reference_arm(args, rank, world, emit):
     if rank != 0:
         return
     threads = host_threads()
@@ -118,7 +118,7 @@ def run_reference_arm(args, rank, world):
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "ms_per_step is the time one full pass would take at the sampled rate",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -170,7 +170,7 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- our arm
-def run_ours(args, rank, world, local_rank):
+def run_ours(args, rank, world, local_rank, emit):
     import torch
     from tensorax_b200 import _lib
 
@@ -289,12 +289,23 @@ def run_ours(args, rank, world, local_rank):
                          "sample": f"{threads} concurrent (b,h) slices x 2048 query rows x all {S} keys "
                                    f"({threads * 2048 / (B * H * S):.4f} of one pass), {cpu_dt:.1f} s"},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
 
 def main():
+    # Libraries (NCCL prints its version banner on stdout) must not get between the driver and the
+    # one JSON line: everything written to fd 1 goes to stderr until the line itself is printed.
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line: dict) -> None:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -311,11 +322,12 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
                os.path.abspath(__file__)] + sys.argv[1:]
+        os.dup2(real_stdout, 1)
         raise SystemExit(subprocess.call(cmd))
     if args.impl == "reference":
-        run_reference_arm(args, rank, world)
+        run_reference_arm(args, rank, world, emit)
         return
-    run_ours(args, rank, world, local_rank)
+    run_ours(args, rank, world, local_rank, emit)
 
 
 if __name__ == "__main__":

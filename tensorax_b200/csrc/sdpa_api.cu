@@ -203,17 +203,26 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
+    const int tune = (d->flags >> 3) & 7;     // tuning switch while the polynomial share is characterised
     switch (d->d_k) {
     case 64:
+        if (tune == 1) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 1>>(d, st, status);
+        if (tune == 2) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 2>>(d, st, status);
+        if (tune == 3) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 3>>(d, st, status);
+        if (tune == 4) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 4>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
     case 128:
+        if (tune == 1) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 1>>(d, st, status);
+        if (tune == 2) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 2>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:
+        if (tune == 1) return launch_tc_t<txb::TcCfg<256, 256, 128, 1, true, false, 0, 1>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true>>(d, st, status);
     case 512:
+        if (tune == 1) return launch_tc_t<txb::TcCfg<512, 256, 64, 1, true, false, 0, 1>>(d, st, status);
         return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true>>(d, st, status);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);

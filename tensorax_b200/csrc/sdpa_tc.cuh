@@ -70,13 +70,18 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int POLY_ = 0, int NSV_ = NS_>
 struct TcCfg {
     static constexpr bool PROF = PROF_;   // collect the section profile
+    // POLY = n > 0: of every 16 exponentials, n are evaluated by a polynomial on the FMA pipe
+    // instead of the special-function unit (16 results per clock and SM), which is the busiest
+    // pipe of this kernel at small head dims.
+    static constexpr int POLY = POLY_;
     static constexpr int DK = DK_;        // head dim of Q and K
     static constexpr int DV = DV_;        // value columns this CTA owns
     static constexpr int BN = BN_;        // keys per tile
-    static constexpr int NS = NS_;        // K/V ring depth
+    static constexpr int NS = NS_;        // K ring depth
+    static constexpr int NSV = NSV_;      // V ring depth
     static constexpr bool P_TMEM = P_TMEM_;
     static constexpr int BM = 128;        // query rows per CTA
     static constexpr int SOFTMAX_WARPS = 4;
@@ -91,10 +96,10 @@ struct TcCfg {
     static constexpr uint32_t OFF_Q = 0;
     static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
     static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
-    static constexpr uint32_t OFF_P = OFF_V + NS * V_BYTES;
+    static constexpr uint32_t OFF_P = OFF_V + NSV * V_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
-    // barriers: q_full, s_full, s_free, p_full, pv_done, then k_full/k_empty/v_full/v_empty[NS]
-    static constexpr int N_BARS = 5 + 4 * NS;
+    // barriers: q_full, s_full, s_free, p_full, pv_done, then k_full/k_empty[NS], v_full/v_empty[NSV]
+    static constexpr int N_BARS = 5 + 2 * NS + 2 * NSV;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
@@ -122,7 +127,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const TcParams p)
 {
-    constexpr int DK = Cfg::DK, DV = Cfg::DV, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
+    constexpr int DK = Cfg::DK, DV = Cfg::DV, BN = Cfg::BN, NS = Cfg::NS, NSV = Cfg::NSV, BM = Cfg::BM;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t q_s = sbase + Cfg::OFF_Q, k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V;
@@ -131,7 +136,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t q_full = bar0, s_full = bar0 + 8, s_free = bar0 + 16, p_full = bar0 + 24,
                    pv_done = bar0 + 32;
     const uint32_t k_full = bar0 + 40, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS,
-                   v_empty = v_full + 8 * NS;
+                   v_empty = v_full + 8 * NSV;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
@@ -177,6 +182,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(k_full + 8 * s, 1);
             ptx::mbar_init(k_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < NSV; ++s) {
             ptx::mbar_init(v_full + 8 * s, 1);
             ptx::mbar_init(v_empty + 8 * s, 1);
         }
@@ -230,16 +237,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                          k_full + 8 * s, pn * 64, j * BN, kvh);
                 }
                 __syncwarp();
+                const int sv_ = j % NSV;
+                const uint32_t phv = (uint32_t)(j / NSV) & 1u;
                 tick(0);
-                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                ok = ptx::mbar_wait(v_empty + 8 * sv_, phv ^ 1u, abort_flag);
                 tick(2);
                 if (!ok) break;
                 if (leader) {
-                    ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
+                    ptx::mbar_arrive_expect_tx(v_full + 8 * sv_, Cfg::V_BYTES);
 #pragma unroll
                     for (int pn = 0; pn < Cfg::VP; ++pn)
-                        ptx::tma_load_3d(v_s + s * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
-                                         v_full + 8 * s, dv0 + pn * 64, j * BN, kvh);
+                        ptx::tma_load_3d(v_s + sv_ * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                         v_full + 8 * sv_, dv0 + pn * 64, j * BN, kvh);
                 }
                 __syncwarp();
             }
@@ -302,8 +311,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tick(2);
                     if (!ok) break;
                 }
-                const int s = j % NS;
-                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                const int s = j % NSV;
+                const uint32_t ph = (uint32_t)(j / NSV) & 1u;
                 tick(0);
                 ok = ptx::mbar_wait(v_full + 8 * s, ph, abort_flag);
                 tick(3);
@@ -420,8 +429,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                              scale2, negm2);
                 const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
                                              scale2, negm2);
-                const float2 ea = make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
-                const float2 eb = make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                // which elements of a group of 16 go to the polynomial is fixed at compile time
+                const int slot = (i / 4) & 3;       // which quad of the group of 16 this is
+                const bool pa_y = Cfg::POLY >= 1 && slot == 0, pb_y = Cfg::POLY >= 2 && slot == 2;
+                const bool pa_x = Cfg::POLY >= 3 && slot == 1, pb_x = Cfg::POLY >= 4 && slot == 3;
+                const float2 ea = make_float2(pa_x ? ptx::ex2_poly(xa.x) : ptx::ex2_approx(xa.x),
+                                              pa_y ? ptx::ex2_poly(xa.y) : ptx::ex2_approx(xa.y));
+                const float2 eb = make_float2(pb_x ? ptx::ex2_poly(xb.x) : ptx::ex2_approx(xb.x),
+                                              pb_y ? ptx::ex2_poly(xb.y) : ptx::ex2_approx(xb.y));
                 sum_a = __fadd2_rn(sum_a, ea);
                 sum_b = __fadd2_rn(sum_b, eb);
                 pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
