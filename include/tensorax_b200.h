@@ -59,8 +59,11 @@ TX_API int tx_cuda_is_available(void);
  * the reference never leaves device 0) */
 TX_API int tx_cuda_device_count(void);
 TX_API int tx_cuda_set_device(int device);
+/* allocations come from the device's stream-ordered pool on the default stream; freed blocks stay
+ * cached in the pool (the reference pays a cudaMalloc/cudaFree pair per output tensor) */
 TX_API void *tx_cuda_malloc(size_t bytes);            /* NULL on failure */
 TX_API int tx_cuda_free(void *ptr);
+TX_API int tx_cuda_pool_trim(void);                   /* give cached blocks back to the driver */
 TX_API int tx_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes);
 TX_API int tx_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes);
 TX_API int tx_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes);

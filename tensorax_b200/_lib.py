@@ -22,7 +22,7 @@ TX_SDPA_P_IN_SMEM = 2
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (
     "tx_last_error", "tx_version",
-    "tx_cuda_is_available", "tx_cuda_device_count", "tx_cuda_set_device", "tx_cuda_malloc", "tx_cuda_free", "tx_cuda_memcpy_h2d",
+    "tx_cuda_is_available", "tx_cuda_device_count", "tx_cuda_set_device", "tx_cuda_malloc", "tx_cuda_free", "tx_cuda_pool_trim", "tx_cuda_memcpy_h2d",
     "tx_cuda_memcpy_d2h", "tx_cuda_memcpy_d2d", "tx_cuda_synchronize",
     "tx_host_alloc_pinned", "tx_host_free_pinned",
     "tx_sdpa_naive_cuda", "tx_sdpa_tiled_cuda", "tx_sdpa_flash_cuda",

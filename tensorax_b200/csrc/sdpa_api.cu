@@ -197,32 +197,28 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     return TX_OK;
 }
 
+// Elements (bit e = element e of each group of 16) whose exponential is evaluated by the FMA-pipe
+// polynomial at d = 64; measured round-robin against 0, 1, 3 and 4 of 16 and other placements.
+constexpr int kPolyMaskD64 = 0x0202;
+
 // Tile shapes per head dim (template arguments: DK, DV per CTA, keys per tile, ring depth, P in TMEM).
 //   d= 64: 128 keys/tile, two CTAs per SM      d=128: 64 keys/tile, two CTAs per SM
 //   d=256: 64 keys/tile, one CTA per SM        d=512: 32 keys/tile, two CTAs split the value columns
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
-    const int tune = (d->flags >> 3) & 7;     // tuning switch while the polynomial share is characterised
     switch (d->d_k) {
     case 64:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 1>>(d, st, status);
-        if (tune == 2) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 2>>(d, st, status);
-        if (tune == 3) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 3>>(d, st, status);
-        if (tune == 4) return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, 4>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
-        return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true>>(d, st, status);
+        // d = 64 is bound by the special-function pipe: 2 of every 16 exponentials go to the FMA pipe
+        return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, kPolyMaskD64>>(d, st, status);
     case 128:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 1>>(d, st, status);
-        if (tune == 2) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, false, 2>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<256, 256, 128, 1, true, false, 0, 1>>(d, st, status);
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
         return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true>>(d, st, status);
     case 512:
-        if (tune == 1) return launch_tc_t<txb::TcCfg<512, 256, 64, 1, true, false, 0, 1>>(d, st, status);
         return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true>>(d, st, status);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
@@ -390,6 +386,27 @@ int static_scratch(unsigned char **out)
     return TX_OK;
 }
 
+// Output tensors are allocated per call by the dispatchers (csrc/tensor_ops.cpp:901-907), and in the
+// reference every one of them is a cudaMalloc / cudaFree pair -- device-wide synchronisations that
+// dominate short calls (docs/profiling/RESULTS.md:149-152).  Here the pair goes through the device's
+// stream-ordered memory pool with a release threshold that keeps freed blocks cached, so a steady
+// sequence of calls stops touching the driver's allocator after the first one.
+int pool_ready()
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    static bool ready[kMaxDevices] = {};
+    if (dev < 0 || dev >= kMaxDevices) return fail(TX_ERR_INVALID, "device index %d out of range", dev);
+    if (!ready[dev]) {
+        cudaMemPool_t pool;
+        TX_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+        unsigned long long keep = ~0ull;
+        TX_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        ready[dev] = true;
+    }
+    return TX_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -426,9 +443,10 @@ int tx_cuda_set_device(int device)
 void *tx_cuda_malloc(size_t bytes)
 {
     void *p = nullptr;
-    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (pool_ready() != TX_OK) return nullptr;
+    cudaError_t e = cudaMallocAsync(&p, bytes ? bytes : 1, (cudaStream_t)0);
     if (e != cudaSuccess) {
-        fail(TX_ERR_CUDA, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+        fail(TX_ERR_CUDA, "cudaMallocAsync(%zu) failed: %s", bytes, cudaGetErrorString(e));
         (void)cudaGetLastError();
         return nullptr;
     }
@@ -438,7 +456,18 @@ void *tx_cuda_malloc(size_t bytes)
 int tx_cuda_free(void *ptr)
 {
     if (!ptr) return TX_OK;
-    TX_CUDA(cudaFree(ptr));
+    TX_CUDA(cudaFreeAsync(ptr, (cudaStream_t)0));
+    return TX_OK;
+}
+
+int tx_cuda_pool_trim(void)
+{
+    int dev = 0;
+    TX_CUDA(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    TX_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    TX_CUDA(cudaDeviceSynchronize());
+    TX_CUDA(cudaMemPoolTrimTo(pool, 0));
     return TX_OK;
 }
 
@@ -600,7 +629,7 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     int rc = TX_OK;
     if (cudaMemsetAsync(dev, 0, 32 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
     if (rc == TX_OK) {
-        if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true>>(d, st, status, dev);
+        if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, kPolyMaskD64>>(d, st, status, dev);
         else rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
     }
     if (rc == TX_OK) rc = finish(st);

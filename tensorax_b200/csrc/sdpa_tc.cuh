@@ -73,9 +73,9 @@ enum TcStatus : int {
 template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int POLY_ = 0, int NSV_ = NS_>
 struct TcCfg {
     static constexpr bool PROF = PROF_;   // collect the section profile
-    // POLY = n > 0: of every 16 exponentials, n are evaluated by a polynomial on the FMA pipe
-    // instead of the special-function unit (16 results per clock and SM), which is the busiest
-    // pipe of this kernel at small head dims.
+    // POLY: bit e set = element e of every group of 16 exponentials is evaluated by a polynomial
+    // on the FMA pipe instead of the special-function unit (16 results per clock and SM), which
+    // is the busiest pipe of this kernel at small head dims.
     static constexpr int POLY = POLY_;
     static constexpr int DK = DK_;        // head dim of Q and K
     static constexpr int DV = DV_;        // value columns this CTA owns
@@ -430,9 +430,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
                                              scale2, negm2);
                 // which elements of a group of 16 go to the polynomial is fixed at compile time
-                const int slot = (i / 4) & 3;       // which quad of the group of 16 this is
-                const bool pa_y = Cfg::POLY >= 1 && slot == 0, pb_y = Cfg::POLY >= 2 && slot == 2;
-                const bool pa_x = Cfg::POLY >= 3 && slot == 1, pb_x = Cfg::POLY >= 4 && slot == 3;
+                const int e0 = i & 15;
+                const bool pa_x = (Cfg::POLY >> e0) & 1, pa_y = (Cfg::POLY >> (e0 + 1)) & 1;
+                const bool pb_x = (Cfg::POLY >> (e0 + 2)) & 1, pb_y = (Cfg::POLY >> (e0 + 3)) & 1;
                 const float2 ea = make_float2(pa_x ? ptx::ex2_poly(xa.x) : ptx::ex2_approx(xa.x),
                                               pa_y ? ptx::ex2_poly(xa.y) : ptx::ex2_approx(xa.y));
                 const float2 eb = make_float2(pb_x ? ptx::ex2_poly(xb.x) : ptx::ex2_approx(xb.x),
