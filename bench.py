@@ -47,8 +47,8 @@ ALG_BYTES_PER_STEP = B * H * S * D * (2 + 2 + 2 + 4)        # Q,K,V fp16 reads +
 METRIC = "fp16 SDPA fwd TFLOP/s per GPU at B4 H8 S8192 d64; % of B200 dense fp16 peak"
 PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070 Ti Laptop (sm_86)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel: mean of the two
-# launches captured with `ncu --set full` (profiles/sdpa_tc_kernel_config2_d64.md: 135.87 MB, 137.68 MB)
-NCU_DRAM_BYTES_PER_LAUNCH = 136_770_000
+# launches captured with `ncu --set full` (profiles/sdpa_tc_kernel_config2_d64.md: 137.14 MB, 136.12 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 136_630_000
 WORKLOAD = "config2: SDPA fwd fp16 (fp32 accumulate) B=4 H=8 S=8192 d=64 non-causal, no mask"
 
 
@@ -123,22 +123,64 @@ def run_reference_arm(args, rank, world, emit):
 
 # ----------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML (read-only) from a thread while the timed
+    region runs; falls back to one `nvidia-smi --query-gpu` loop if NVML cannot be imported."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        import threading
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
         self.proc = None
+        self.tmp = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.tmp, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[gpu_index]) if visible and visible.split(",")[gpu_index].isdigit() else gpu_index
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        r = get_reasons(h)
+                        for name, bit in bits.items():
+                            if r & bit:
+                                self.reasons.add(name)
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self._thread = threading.Thread(target=poll, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._thread = None
+            self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "20"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+            except OSError:
+                self.proc = None
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": "nvml"}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            if self.sm:
+                out.update(sm_mhz=statistics.median(self.sm), sm_max_mhz=self.max_mhz,
+                           reasons=sorted(self.reasons), samples=len(self.sm))
+            return out
+        out["source"] = "nvidia-smi"
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -282,7 +324,7 @@ def run_ours(args, rank, world, local_rank, emit):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_src,
-                     "kernel": "sdpa_tc_kernel<D=64,BN=128>", "flops_per_launch": FLOPS_PER_STEP,
+                     "kernel": "sdpa_tc_kernel<DK=64,DV=64,BN=128,NS=3>", "flops_per_launch": FLOPS_PER_STEP,
                      "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP,
                      "hbm_gbs_algorithmic": ALG_BYTES_PER_STEP / (kernel_ms * 1e-3) / 1e9},
         "cpu_baseline": {"value": cpu_fl / cpu_dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": cpu_kind,
