@@ -61,6 +61,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of the same condition: answers at once, where try_wait may first park
+// the thread for a while.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  `abort_flag` is a shared-memory word any thread of the CTA sets
 // when it gives up; everybody else then stops waiting at once.  The bound is
 // wall-clock (the nanosecond global timer), not a spin count, because one
@@ -74,6 +90,7 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
 {
+    if (mbar_test_wait(bar, parity)) return true;      // the common case: the phase is already over
     uint64_t t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
