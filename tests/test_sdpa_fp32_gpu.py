@@ -135,3 +135,19 @@ def test_cast_and_repeat_interleave_on_device():
         assert np.array_equal(t.repeat_interleave(3, dim=dim).numpy(), np.repeat(x, 3, axis=dim))
     assert np.array_equal(h.repeat_interleave(2, dim=1).numpy(), np.repeat(x.astype(np.float16), 2, axis=1))
     assert t.cpu().tolist() == x.astype(np.float64).tolist()
+
+
+def test_allocation_pool_reuses_and_trims():
+    """cuda_malloc / cuda_free replacements (csrc/cuda/tensor_cuda.cu:13-21) on the stream-ordered pool."""
+    lib = _lib.load()
+    x = seeded(30, 1 << 16)
+    ptrs = set()
+    for _ in range(20):
+        buf = _lib.to_device(x)
+        assert np.array_equal(buf.download(x.shape, np.float32), x)
+        ptrs.add(buf.ptr)
+        del buf
+    assert len(ptrs) < 20          # freed blocks come back from the pool
+    _lib.check(lib.tx_cuda_pool_trim())
+    buf = _lib.to_device(x)
+    assert np.array_equal(buf.download(x.shape, np.float32), x)
