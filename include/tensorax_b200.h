@@ -120,10 +120,15 @@ TX_API int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, i
  *      x is [batch, seq, in_features], or [batch, heads_in, seq, in_features/heads_in] when
  *      heads_in > 0; out is [batch, seq, out_features], or head-split
  *      [batch, heads_out, seq, out_features/heads_out] when heads_out > 0; W is [out_features,
- *      in_features]; bias may be NULL.  Does not synchronise. */
+ *      in_features]; bias may be NULL.  Does not synchronise (tx_sdpa_finish / tx_cuda_synchronize
+ *      also report a kernel-side failure of this launch).  Shapes whose feature counts (per head,
+ *      where split) are multiples of 32 run on the tensor cores as split-TF32 (three TF32 MMAs per
+ *      product keep fp32-grade accuracy); everything else runs on CUDA cores in exact fp32.
+ *      tx_linear_set_cuda_cores_only(1) forces the latter (testing). */
 TX_API int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float *out,
                               int64_t batch, int64_t seq, int64_t in_features, int64_t out_features,
                               int32_t heads_in, int32_t heads_out);
+TX_API int tx_linear_set_cuda_cores_only(int on);
 
 /* ---- general form (no reference counterpart: the reference has no fp16+mask,
  *      no implicit causal / key-length mask and no grouped K/V heads; its dense

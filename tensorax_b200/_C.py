@@ -193,7 +193,7 @@ def linear(x: TensorImpl, weight: TensorImpl, bias: Optional[TensorImpl] = None,
     lib = _lib.load()
     _lib.check(lib.tx_linear_f32_cuda(x.data_ptr, weight.data_ptr, bias.data_ptr if bias is not None else None,
                                       out.data_ptr, B, S, K, N, int(heads_in), int(heads_out)))
-    _lib.check(lib.tx_cuda_synchronize())
+    _lib.check(lib.tx_sdpa_finish(None))      # waits, and reports a kernel-side failure if there was one
     return out
 
 
@@ -286,6 +286,23 @@ def scaled_dot_product_attention_mma_fp16(query, key, value) -> TensorImpl:
     if query.dtype != "float16" or key.dtype != "float16" or value.dtype != "float16":
         raise RuntimeError("SDPA fp16: all inputs must have dtype float16")
     return _forward(query, key, value, None, who="SDPA fp16")
+
+
+def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
+    """Counterpart of the reference's ``profile_sections_sdpa_*`` bindings
+    (csrc/tensor_ops.cpp:1434-1507, 1622-1636): runs the call once on the instrumented
+    tensor-core kernel (fp16, d = 64 or 128) and returns 32 cycle counters of one CTA; the
+    meaning of each slot is listed beside ``tx_profile_sections_sdpa`` in the C header."""
+    B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, None, "profile_sections")
+    if query.device != "cuda" or query.dtype != "float16":
+        raise RuntimeError("profile_sections: float16 CUDA tensors expected")
+    out = TensorImpl([B, H, Sq, dv], "float32", "cuda")
+    desc = _lib.SdpaDesc(q=query.data_ptr, k=key.data_ptr, v=value.data_ptr, mask=None, kv_lens=None,
+                         out=out.data_ptr, batch=B, q_heads=H, kv_heads=Hkv, seq_q=Sq, seq_k=Sk, d_k=dk,
+                         d_v=dv, dtype=_lib.TX_DTYPE_F16, causal=int(bool(causal)), flags=0, stream=None)
+    ticks = (ctypes.c_longlong * 32)()
+    _lib.check(_lib.load().tx_profile_sections_sdpa(ctypes.byref(desc), ticks))
+    return list(ticks)
 
 
 def scaled_dot_product_attention_ex(query, key, value, mask=None, causal=False, kv_lens=None,

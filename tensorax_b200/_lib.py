@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = (
     "tx_host_alloc_pinned", "tx_host_free_pinned",
     "tx_sdpa_naive_cuda", "tx_sdpa_tiled_cuda", "tx_sdpa_flash_cuda",
     "tx_sdpa_optimized_flash_cuda", "tx_sdpa_mma_cuda", "tx_sdpa_mma_fp16_cuda",
-    "tx_cast_f32_to_f16_cuda", "tx_repeat_interleave_cuda", "tx_linear_f32_cuda",
+    "tx_cast_f32_to_f16_cuda", "tx_repeat_interleave_cuda", "tx_linear_f32_cuda", "tx_linear_set_cuda_cores_only",
     "tx_sdpa_forward", "tx_sdpa_finish", "tx_sdpa_uses_tensor_cores",
     "tx_kernel_launch_count", "tx_profile_sections_sdpa", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
 )
@@ -84,6 +84,7 @@ def load():
     lib.tx_cast_f32_to_f16_cuda.argtypes = [c_void_p, c_void_p, c_int64]
     lib.tx_repeat_interleave_cuda.argtypes = [c_void_p, c_void_p] + [c_int64] * 4 + [c_int32]
     lib.tx_linear_f32_cuda.argtypes = [c_void_p] * 4 + [c_int64] * 4 + [c_int32] * 2
+    lib.tx_linear_set_cuda_cores_only.argtypes = [c_int]
     lib.tx_sdpa_forward.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]

@@ -133,6 +133,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
         : "memory");
 }
 
+// 4-D tile load: coordinates are (innermost element, row, plane, slab).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                            int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- tensor memory
 // Must be executed by one whole warp; the base address lands in shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
@@ -199,6 +210,27 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major)
 {
     return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) |
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Instruction descriptor, kind::tf32: fp32 words in shared memory read as TF32 (format code 2 for
+// A and B), fp32 accumulator, both operands K-major.
+__host__ __device__ constexpr uint32_t idesc_tf32(int m, int n)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+// D[tmem] (+)= A[smem] * B[smem] on TF32 inputs (K = 8 per instruction); issued by ONE thread.
+__device__ __forceinline__ void mma_ss_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

@@ -18,6 +18,7 @@
 #include <vector>
 
 #include "linear_simt.cuh"
+#include "linear_tc.cuh"
 #include "sdpa_simt.cuh"
 #include "sdpa_tc.cuh"
 
@@ -111,6 +112,21 @@ int make_map(CUtensorMap *m, const void *base, int64_t slabs, int64_t rows, int6
                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TX_OK;
+}
+
+// fp32 tensor maps of the linear layer: 128-byte-swizzled boxes of 32 floats x `box_rows` rows.
+int make_map_f32(CUtensorMap *m, const void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
+                 int box_rows)
+{
+    EncodeTiledFn enc;
+    if (int rc = get_encode_fn(&enc)) return rc;
+    cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TX_ERR_CUDA, "cuTensorMapEncodeTiled (fp32) failed with code %d", (int)r);
     return TX_OK;
 }
 
@@ -329,6 +345,9 @@ int workspace(size_t bytes, void **out)
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+std::atomic<int> g_linear_force_simt{0};
+bool flags_linear_force_simt() { return g_linear_force_simt.load() != 0; }
 
 // Streams and events of the host-buffer form, created once per device.
 constexpr int kHostChunks = 8;
@@ -590,6 +609,12 @@ int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t 
     return TX_OK;
 }
 
+int tx_linear_set_cuda_cores_only(int on)
+{
+    g_linear_force_simt.store(on ? 1 : 0);
+    return TX_OK;
+}
+
 int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float *out, int64_t batch,
                        int64_t seq, int64_t in_features, int64_t out_features, int32_t heads_in,
                        int32_t heads_out)
@@ -600,6 +625,40 @@ int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float 
         (heads_out > 0 && out_features % heads_out))
         return fail(TX_ERR_INVALID, "linear: feature count must be a multiple of the head count");
     if (int rc = ensure_device()) return rc;
+    const int64_t dh_in = heads_in > 0 ? in_features / heads_in : in_features;
+    const int64_t dh_out = heads_out > 0 ? out_features / heads_out : out_features;
+    auto al = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const bool tensor_cores = !(flags_linear_force_simt()) && in_features % 32 == 0 && dh_in % 32 == 0 &&
+                              out_features % 32 == 0 && dh_out % 32 == 0 && al(x) && al(w) && al(out) &&
+                              (!bias || al(bias)) && batch <= 65535 && (seq + 127) / 128 <= 65535;
+    if (tensor_cores) {
+        int *status = nullptr;
+        if (int rc = status_word(&status)) return rc;
+        CUtensorMap tx_map, tw_map;
+        const int64_t hin = heads_in > 0 ? heads_in : 1;
+        cuuint64_t xd[4] = {(cuuint64_t)dh_in, (cuuint64_t)seq, (cuuint64_t)hin, (cuuint64_t)batch};
+        cuuint64_t xs[3];
+        if (heads_in > 0) {        // [B, H, S, dh]
+            xs[0] = (cuuint64_t)dh_in * 4; xs[1] = (cuuint64_t)seq * dh_in * 4; xs[2] = (cuuint64_t)hin * seq * dh_in * 4;
+        } else {                   // [B, S, K] seen as one head
+            xs[0] = (cuuint64_t)in_features * 4; xs[1] = (cuuint64_t)seq * in_features * 4; xs[2] = (cuuint64_t)seq * in_features * 4;
+        }
+        if (int rc = make_map_f32(&tx_map, x, 4, xd, xs, txb::LTC_BM)) return rc;
+        cuuint64_t wd[3] = {(cuuint64_t)in_features, (cuuint64_t)out_features, 1};
+        cuuint64_t ws[2] = {(cuuint64_t)in_features * 4, (cuuint64_t)in_features * out_features * 4};
+        if (int rc = make_map_f32(&tw_map, w, 3, wd, ws, txb::LTC_BN)) return rc;
+        txb::LinearTcParams lp;
+        lp.bias = bias; lp.out = out; lp.status = status;
+        lp.S = (int)seq; lp.N = (int)out_features; lp.K = (int)in_features;
+        lp.dh_in = (int)dh_in; lp.heads_out = heads_out;
+        TX_CUDA(cudaFuncSetAttribute(txb::linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)txb::LTC_SMEM));
+        dim3 grid((unsigned)((out_features + txb::LTC_BN - 1) / txb::LTC_BN), (unsigned)((seq + txb::LTC_BM - 1) / txb::LTC_BM),
+                  (unsigned)batch);
+        txb::linear_tc_kernel<<<grid, txb::LTC_THREADS, txb::LTC_SMEM>>>(tx_map, tw_map, lp);
+        g_launches++;
+        TX_CUDA(cudaGetLastError());
+        return TX_OK;
+    }
     txb::LinearParams p;
     p.x = x; p.w = w; p.bias = bias; p.out = out;
     p.B = batch; p.S = seq; p.K = in_features; p.N = out_features;

@@ -21,20 +21,52 @@ def test_linear_golden(golden):
     assert_close_fp32(F.linear(x2, w, b).numpy(), golden["lin_out"][0])
 
 
-@pytest.mark.parametrize("B,S,K,N,H", [(2, 70, 96, 64, 4), (1, 129, 130, 66, 2), (3, 5, 33, 260, 1)])
-def test_linear_with_head_split_and_merge(B, S, K, N, H):
+LINEAR_SHAPES = [
+    (2, 70, 96, 64, 4),       # ragged rows, 16-wide heads: CUDA-core kernel for the head-split forms
+    (1, 129, 130, 66, 2),     # nothing is a multiple of 32: CUDA-core kernel
+    (3, 5, 33, 260, 1),
+    (2, 200, 128, 256, 4),    # multiples of 32 throughout: split-TF32 tensor-core kernel
+    (1, 384, 512, 384, 6),
+    (2, 128, 64, 128, 2),
+]
+
+
+@pytest.mark.parametrize("cuda_cores_only", [False, True])
+@pytest.mark.parametrize("B,S,K,N,H", LINEAR_SHAPES)
+def test_linear_with_head_split_and_merge(B, S, K, N, H, cuda_cores_only):
+    from tensorax_b200 import _lib
+    lib = _lib.load()
     x, w, b = seeded(1, B, S, K), seeded(2, N, K) / np.sqrt(K), seeded(3, N)
     ref = oracle.linear_f32(x, w, b)
     xt, wt, bt = (ts.Tensor(a, device="cuda") for a in (x, w, b))
-    plain = _C.to_numpy(_C.linear(xt._c_tensor, wt._c_tensor, bt._c_tensor))
-    assert_close_fp32(plain, ref)
-    split = _C.to_numpy(_C.linear(xt._c_tensor, wt._c_tensor, bt._c_tensor, heads_out=H))
-    assert split.shape == (B, H, S, N // H)
-    assert np.array_equal(split, plain.reshape(B, S, H, N // H).transpose(0, 2, 1, 3))
-    if K % H == 0:
-        xs = np.ascontiguousarray(x.reshape(B, S, H, K // H).transpose(0, 2, 1, 3))     # what a head-split producer leaves
-        merged = _C.to_numpy(_C.linear(ts.Tensor(xs, device="cuda")._c_tensor, wt._c_tensor, bt._c_tensor, heads_in=H))
-        assert np.array_equal(merged, plain)
+    lib.tx_linear_set_cuda_cores_only(int(cuda_cores_only))
+    try:
+        launches = lib.tx_kernel_launch_count()
+        plain = _C.to_numpy(_C.linear(xt._c_tensor, wt._c_tensor, bt._c_tensor))
+        assert lib.tx_kernel_launch_count() == launches + 1
+        assert_close_fp32(plain, ref)
+        split = _C.to_numpy(_C.linear(xt._c_tensor, wt._c_tensor, bt._c_tensor, heads_out=H))
+        assert split.shape == (B, H, S, N // H)
+        assert_close_fp32(split, ref.reshape(B, S, H, N // H).transpose(0, 2, 1, 3))
+        if K % H == 0:
+            xs = np.ascontiguousarray(x.reshape(B, S, H, K // H).transpose(0, 2, 1, 3))   # what a head-split producer leaves
+            merged = _C.to_numpy(_C.linear(ts.Tensor(xs, device="cuda")._c_tensor, wt._c_tensor, bt._c_tensor, heads_in=H))
+            assert_close_fp32(merged, ref)
+        nobias = _C.to_numpy(_C.linear(xt._c_tensor, wt._c_tensor, None))
+        assert_close_fp32(nobias, oracle.linear_f32(x, w))
+    finally:
+        lib.tx_linear_set_cuda_cores_only(0)
+
+
+def test_split_tf32_keeps_fp32_accuracy_on_hard_inputs():
+    """Values whose low mantissa bits matter: a plain TF32 product would be off by ~1e-3 here."""
+    B, S, K, N = 1, 256, 1024, 128
+    x = (1.0 + seeded(40, B, S, K) * 1e-3).astype(np.float32)        # 1.000xxx: the information sits below TF32's 10 bits
+    w = (seeded(41, N, K) / K).astype(np.float32)
+    got = _C.to_numpy(_C.linear(ts.Tensor(x, device="cuda")._c_tensor, ts.Tensor(w, device="cuda")._c_tensor, None))
+    ref64 = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(got - ref64).max() <= 2e-6
+    assert_close_fp32(got, oracle.linear_f32(x, w))
 
 
 def test_multi_head_attention_forward_golden(golden):

@@ -233,3 +233,15 @@ def test_sharded_runs_equal_the_single_device_run_bitwise():
             loc, _ = sdpa_device(qs, ks, vs, causal=True, kv_lens=ls)
             sharding.place_output(sh, out, loc)
         assert np.array_equal(out.view(np.uint32), full.view(np.uint32))
+
+
+def test_section_profile_entry_point():
+    """profile_sections_sdpa_* of the reference (csrc/tensor_ops.cpp:1434-1507): 32 counters, sane values."""
+    from tensorax_b200 import _C
+    B, H, S, d = 1, 2, 1024, 64
+    q, k, v = (_C.from_numpy(seeded(90 + j, B, H, S, d).astype(np.float16), "cuda") for j in range(3))
+    t = _C.profile_sections_sdpa(q, k, v)
+    assert len(t) == 32 and t[10] == S // 128                  # key tiles walked by CTA (0,0,0)
+    assert t[0] > 0 and t[16] > 0 and t[24] > 0                # softmax, MMA and producer lanes all reported
+    assert t[5] > t[3] > 0                                     # exponentials cost more than the row max
+    assert sum(t[1:9]) <= t[0] * 1.05
