@@ -12,6 +12,14 @@
 // rounding of lo are of order 2^-21 relative, which keeps the result within 1e-5 of the
 // reference's fp32 matmul.
 //
+// The tensor core adds into its fp32 accumulator with truncation, so a long chain of
+// accumulations drifts by about one ulp per step, always downwards in magnitude (measured:
+// 2.3e-5 at K = 512 with every MMA on one accumulator).  The chain is therefore kept short: the
+// two correction products go to an accumulator of their own (they are 2^-10 of the result, their
+// drift does not matter) and the main product rotates over three accumulators; the epilogue adds
+// the four partial sums with ordinary round-to-nearest fp32 adds.  4 x 128 columns = all of
+// tensor memory, one CTA per SM.
+//
 // One CTA = 128 rows of one batch element x 128 output features.  Six warps:
 //   warp 0     TMA producer: x tile [128 rows][32 k] and W tile [128 features][32 k] per stage
 //              (fp32, 128-byte rows, 128-byte swizzle); x is addressed through a 4-D map
@@ -71,7 +79,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if ((sbase & 1023u) || *reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), 128);
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
         ptx::tmem_relinquish();
     }
     ptx::tc_fence_before_sync();
@@ -119,11 +127,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                     for (int k8 = 0; k8 < LTC_BK / 8; ++k8) {
                         const uint32_t x_hi = st_lo + ((k8 * 32) >> 4), w_hi = x_hi + (LTC_TILE >> 4);
                         const uint32_t x_lo = x_hi + (2 * LTC_TILE >> 4), w_lo = x_hi + (3 * LTC_TILE >> 4);
-                        // small terms first, then the main product
-                        ptx::mma_ss_tf32(tmem, ptx::make_desc(x_lo, desc_hi), ptx::make_desc(w_hi, desc_hi), idesc,
+                        // columns [0,384): three main accumulators used in rotation; [384,512): corrections
+                        const uint32_t d_main = tmem + (uint32_t)(kt % 3) * 128, d_corr = tmem + 384;
+                        ptx::mma_ss_tf32(d_corr, ptx::make_desc(x_lo, desc_hi), ptx::make_desc(w_hi, desc_hi), idesc,
                                          (kt > 0 || k8 > 0) ? 1u : 0u);
-                        ptx::mma_ss_tf32(tmem, ptx::make_desc(x_hi, desc_hi), ptx::make_desc(w_lo, desc_hi), idesc, 1u);
-                        ptx::mma_ss_tf32(tmem, ptx::make_desc(x_hi, desc_hi), ptx::make_desc(w_hi, desc_hi), idesc, 1u);
+                        ptx::mma_ss_tf32(d_corr, ptx::make_desc(x_hi, desc_hi), ptx::make_desc(w_lo, desc_hi), idesc, 1u);
+                        ptx::mma_ss_tf32(d_main, ptx::make_desc(x_hi, desc_hi), ptx::make_desc(w_hi, desc_hi), idesc,
+                                         (kt >= 3 || k8 > 0) ? 1u : 0u);
                     }
                     ptx::mma_commit(empty + 8 * s);
                     if (kt == k_tiles - 1) ptx::mma_commit(acc_done);
@@ -165,11 +175,20 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 const int row = s0 + quarter * 32 + lane;
                 const uint32_t t_acc = tmem + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
+                const int n_main = k_tiles < 3 ? k_tiles : 3;      // main accumulators that were written
                 for (int c = 0; c < LTC_BN / 32; ++c) {
                     uint32_t v[32];
-                    ptx::tmem_ld32(t_acc + c * 32, v);
+                    ptx::tmem_ld32(t_acc + 384 + c * 32, v);            // corrections first, then the main sums
                     ptx::tmem_wait_ld();
                     ptx::reg_fence32(v);
+                    for (int a = 0; a < n_main; ++a) {
+                        uint32_t u[32];
+                        ptx::tmem_ld32(t_acc + a * 128 + c * 32, u);
+                        ptx::tmem_wait_ld();
+                        ptx::reg_fence32(u);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(u[i]));
+                    }
                     const int n = n0 + c * 32;
                     if (row < p.S && n < p.N) {
                         float *dst;
@@ -204,7 +223,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem, 128);
+        ptx::tmem_dealloc(tmem, 512);
     }
 }
 
