@@ -184,6 +184,10 @@ int launch_simt(const txb::SimtParams &p, cudaStream_t st)
     return launch_simt_t<T, 8>(p, st);   // wider heads: one CTA column per 256 value columns
 }
 
+// Elements (bit e = element e of each group of 16) whose exponential is evaluated by the FMA-pipe
+// polynomial at d = 64; measured round-robin against 0, 1, 3 and 4 of 16 and other placements.
+constexpr int kPolyMaskD64 = 0x0202;
+
 template <class Cfg>
 int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
 {
@@ -213,10 +217,6 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     return TX_OK;
 }
 
-// Elements (bit e = element e of each group of 16) whose exponential is evaluated by the FMA-pipe
-// polynomial at d = 64; measured round-robin against 0, 1, 3 and 4 of 16 and other placements.
-constexpr int kPolyMaskD64 = 0x0202;
-
 // Tile shapes per head dim (template arguments: DK, DV per CTA, keys per tile, ring depth, P in TMEM).
 //   d= 64: 128 keys/tile, two CTAs per SM      d=128: 64 keys/tile, two CTAs per SM
 //   d=256: 64 keys/tile, one CTA per SM        d=512: 32 keys/tile, two CTAs split the value columns
@@ -233,9 +233,12 @@ int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
         return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
     case 256:
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
-        return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true>>(d, st, status);
+        // Narrow key tiles make the A (Q) read the busiest user of the shared-memory port: Q lives
+        // in tensor memory instead, and K / V are fetched as two independent queues.
+        return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, false, 0, 2, true, 128>>(d, st, status);
     case 512:
-        return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true>>(d, st, status);
+        // 496 of 512 tensor-memory columns: S 32 | O 256 | P 16 | first 384 elements of Q 192
+        return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true, false, 0, 2, true, 192>>(d, st, status);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
 }
@@ -677,8 +680,8 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
 {
     if (!ticks32) return fail(TX_ERR_INVALID, "profile_sections: null output");
     if (int rc = validate(d)) return rc;
-    if (!tc_eligible(d) || (d->d_k != 64 && d->d_k != 128))
-        return fail(TX_ERR_UNSUPPORTED, "profile_sections: built for the tensor-core kernel at d = 64 and d = 128");
+    if (!tc_eligible(d))
+        return fail(TX_ERR_UNSUPPORTED, "profile_sections: built for the tensor-core kernel only");
     if (int rc = ensure_device()) return rc;
     int *status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -689,7 +692,9 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     if (cudaMemsetAsync(dev, 0, 32 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
     if (rc == TX_OK) {
         if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, kPolyMaskD64>>(d, st, status, dev);
-        else rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
+        else if (d->d_k == 128) rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
+        else if (d->d_k == 256) rc = launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, dev);
+        else rc = launch_tc_t<txb::TcCfg<512, 256, 32, 2, true, true, 0, 2, true, 192>>(d, st, status, dev);
     }
     if (rc == TX_OK) rc = finish(st);
     if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)

@@ -70,9 +70,17 @@ enum TcStatus : int {
     TC_ERR_SOFTMAX = 4,
 };
 
-template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int POLY_ = 0, int NSV_ = NS_>
+template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int POLY_ = 0, int NSV_ = NS_,
+          bool LD_SPLIT_ = false, int QT_ = 0>
 struct TcCfg {
+    // QT: tensor-memory columns that hold the first 2*QT elements of every Q row (fp16 pairs).
+    // The QK^T MMAs over that part take A from tensor memory, so they read only the K tile from
+    // shared memory; with narrow key tiles the A read is what the shared-memory port runs out of.
+    static constexpr int QT = QT_;
     static constexpr bool PROF = PROF_;   // collect the section profile
+    // LD_SPLIT: the producer serves the K ring and the V ring as two independent queues (a K
+    // tile never waits behind a V stage that is still being read, nor the reverse).
+    static constexpr bool LD_SPLIT = LD_SPLIT_;
     // POLY: bit e set = element e of every group of 16 exponentials is evaluated by a polynomial
     // on the FMA pipe instead of the special-function unit (16 results per clock and SM), which
     // is the busiest pipe of this kernel at small head dims.
@@ -98,8 +106,8 @@ struct TcCfg {
     static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
     static constexpr uint32_t OFF_P = OFF_V + NSV * V_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
-    // barriers: q_full, s_full, s_free, p_full, pv_done, then k_full/k_empty[NS], v_full/v_empty[NSV]
-    static constexpr int N_BARS = 5 + 2 * NS + 2 * NSV;
+    // barriers: q_full, s_full, s_free, p_full, pv_done, q_tmem, then k_full/k_empty[NS], v_full/v_empty[NSV]
+    static constexpr int N_BARS = 6 + 2 * NS + 2 * NSV;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
@@ -107,7 +115,9 @@ struct TcCfg {
     static constexpr uint32_t COL_S = 0;
     static constexpr uint32_t COL_O = BN;
     static constexpr uint32_t COL_P = BN + DV;
-    static constexpr uint32_t COLS_USED = BN + DV + (P_TMEM ? BN / 2 : 0);
+    static constexpr uint32_t COL_Q = BN + DV + (P_TMEM ? BN / 2 : 0);
+    static constexpr uint32_t COLS_USED = COL_Q + QT;
+    static_assert(QT % 32 == 0 && 2 * QT <= DK, "Q columns in tensor memory come in whole 64-element panels");
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 32 ? 32 : COLS_USED <= 64 ? 64
                                         : COLS_USED <= 128 ? 128 : COLS_USED <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
@@ -134,8 +144,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t p_s = sbase + Cfg::OFF_P;
     const uint32_t bar0 = sbase + Cfg::OFF_BAR;
     const uint32_t q_full = bar0, s_full = bar0 + 8, s_free = bar0 + 16, p_full = bar0 + 24,
-                   pv_done = bar0 + 32;
-    const uint32_t k_full = bar0 + 40, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS,
+                   pv_done = bar0 + 32, q_tmem = bar0 + 40;
+    const uint32_t k_full = bar0 + 48, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS,
                    v_empty = v_full + 8 * NSV;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
@@ -175,6 +185,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tid == 0) {
         *abort_flag = 0;
         ptx::mbar_init(q_full, 1);
+        ptx::mbar_init(q_tmem, Cfg::SOFTMAX_WARPS);
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(s_free, Cfg::SOFTMAX_WARPS);     // one arrival per softmax warp
         ptx::mbar_init(p_full, Cfg::SOFTMAX_WARPS);
@@ -222,35 +233,85 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = true;
             tick_start();
             const long long t_begin = Cfg::PROF ? clock64() : 0;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % NS;
-                const uint32_t ph = (uint32_t)(j / NS) & 1u;
-                tick(0);
-                ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
-                tick(1);
-                if (!ok) break;
-                if (leader) {
-                    ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+            if constexpr (Cfg::LD_SPLIT) {
+                // Two queues polled in turn; neither blocks the other.  A stage's "empty" phase
+                // cannot flip again before this warp re-arms it, so any lane seeing it is enough.
+                int jk = 0, jv = 0;
+                uint64_t t_idle = 0;
+                uint32_t spins = 0;
+                while ((jk < n_tiles || jv < n_tiles) && ok) {
+                    bool moved = false;
+                    if (jk < n_tiles) {
+                        const int s = jk % NS;
+                        const uint32_t ph = (uint32_t)(jk / NS) & 1u;
+                        if (__any_sync(0xffffffffu, ptx::mbar_test_wait(k_empty + 8 * s, ph ^ 1u))) {
+                            if (leader) {
+                                ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
 #pragma unroll
-                    for (int pn = 0; pn < Cfg::KP; ++pn)
-                        ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
-                                         k_full + 8 * s, pn * 64, j * BN, kvh);
-                }
-                __syncwarp();
-                const int sv_ = j % NSV;
-                const uint32_t phv = (uint32_t)(j / NSV) & 1u;
-                tick(0);
-                ok = ptx::mbar_wait(v_empty + 8 * sv_, phv ^ 1u, abort_flag);
-                tick(2);
-                if (!ok) break;
-                if (leader) {
-                    ptx::mbar_arrive_expect_tx(v_full + 8 * sv_, Cfg::V_BYTES);
+                                for (int pn = 0; pn < Cfg::KP; ++pn)
+                                    ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
+                                                     k_full + 8 * s, pn * 64, jk * BN, kvh);
+                            }
+                            __syncwarp();
+                            ++jk;
+                            moved = true;
+                        }
+                    }
+                    if (jv < n_tiles) {
+                        const int sv_ = jv % NSV;
+                        const uint32_t phv = (uint32_t)(jv / NSV) & 1u;
+                        if (__any_sync(0xffffffffu, ptx::mbar_test_wait(v_empty + 8 * sv_, phv ^ 1u))) {
+                            if (leader) {
+                                ptx::mbar_arrive_expect_tx(v_full + 8 * sv_, Cfg::V_BYTES);
 #pragma unroll
-                    for (int pn = 0; pn < Cfg::VP; ++pn)
-                        ptx::tma_load_3d(v_s + sv_ * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
-                                         v_full + 8 * sv_, dv0 + pn * 64, j * BN, kvh);
+                                for (int pn = 0; pn < Cfg::VP; ++pn)
+                                    ptx::tma_load_3d(v_s + sv_ * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                                     v_full + 8 * sv_, dv0 + pn * 64, jv * BN, kvh);
+                            }
+                            __syncwarp();
+                            ++jv;
+                            moved = true;
+                        }
+                    }
+                    if (moved) { spins = 0; t_idle = 0; }
+                    else if ((++spins & 127u) == 0u) {
+                        if (*abort_flag) ok = false;
+                        const uint64_t now = ptx::global_timer_ns();
+                        if (t_idle == 0) t_idle = now;
+                        else if (now - t_idle > ptx::kWaitLimitNs) ok = false;
+                    }
                 }
-                __syncwarp();
+            } else {
+                for (int j = 0; j < n_tiles && ok; ++j) {
+                    const int s = j % NS;
+                    const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                    tick(0);
+                    ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
+                    tick(1);
+                    if (!ok) break;
+                    if (leader) {
+                        ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+#pragma unroll
+                        for (int pn = 0; pn < Cfg::KP; ++pn)
+                            ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k,
+                                             k_full + 8 * s, pn * 64, j * BN, kvh);
+                    }
+                    __syncwarp();
+                    const int sv_ = j % NSV;
+                    const uint32_t phv = (uint32_t)(j / NSV) & 1u;
+                    tick(0);
+                    ok = ptx::mbar_wait(v_empty + 8 * sv_, phv ^ 1u, abort_flag);
+                    tick(2);
+                    if (!ok) break;
+                    if (leader) {
+                        ptx::mbar_arrive_expect_tx(v_full + 8 * sv_, Cfg::V_BYTES);
+#pragma unroll
+                        for (int pn = 0; pn < Cfg::VP; ++pn)
+                            ptx::tma_load_3d(v_s + sv_ * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v,
+                                             v_full + 8 * sv_, dv0 + pn * 64, j * BN, kvh);
+                    }
+                    __syncwarp();
+                }
             }
             if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
             if constexpr (Cfg::PROF) {
@@ -277,6 +338,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t v_lo = ptx::smem_desc_sw128_lo(v_s, Cfg::KV_PANEL);
             const uint32_t p_lo = ptx::smem_desc_sw128_lo(p_s, 16);
             bool ok = ptx::mbar_wait(q_full, 0, abort_flag);
+            if constexpr (Cfg::QT > 0) {
+                if (ok) ok = ptx::mbar_wait(q_tmem, 0, abort_flag);
+                ptx::tc_fence_after_sync();
+            }
+            const uint32_t t_q = tmem + Cfg::COL_Q;
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
@@ -288,8 +354,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int kk = 0; kk < DK / 16; ++kk) {
                         const uint32_t qa = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
                         const uint32_t kb = ((kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32) >> 4;
-                        ptx::mma_ss(t_s, ptx::make_desc(q_lo + qa, desc_hi), ptx::make_desc(ks_lo + kb, desc_hi),
-                                    idesc_qk, kk > 0);
+                        if (kk * 8 < Cfg::QT)
+                            ptx::mma_ts(t_s, t_q + kk * 8, ptx::make_desc(ks_lo + kb, desc_hi), idesc_qk, kk > 0);
+                        else
+                            ptx::mma_ss(t_s, ptx::make_desc(q_lo + qa, desc_hi), ptx::make_desc(ks_lo + kb, desc_hi),
+                                        idesc_qk, kk > 0);
                     }
                     ptx::mma_commit(k_empty + 8 * s);
                     ptx::mma_commit(s_full);
@@ -379,6 +448,25 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar);
         };
+        if constexpr (Cfg::QT > 0) {
+            // Copy this thread's Q row (its first 2*QT elements) from the swizzled panels in shared
+            // memory into tensor memory, where the QK^T MMAs read it as their A operand.
+            if (ok) ok = wait_all(q_full, 0);
+            if (ok) {
+#pragma unroll 1
+                for (int pn = 0; pn < Cfg::QT / 32; ++pn) {
+                    uint32_t qv[32];
+                    const uint32_t rowaddr = q_s + (uint32_t)pn * (BM * 128) + (uint32_t)r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        ptx::ld_shared_v4(rowaddr + (uint32_t)((c ^ (r & 7)) << 4), qv[4 * c], qv[4 * c + 1],
+                                          qv[4 * c + 2], qv[4 * c + 3]);
+                    ptx::tmem_st_cols<32>(tmem + lane_base + Cfg::COL_Q + (uint32_t)pn * 32, qv);
+                }
+                ptx::tmem_wait_st();
+            }
+            arrive_warp(q_tmem);
+        }
         tick_start();
         const long long t_begin = Cfg::PROF ? clock64() : 0;
         for (int j = 0; j < n_tiles && ok; ++j) {
