@@ -44,6 +44,8 @@ enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
 /* flags of tx_sdpa_desc */
 enum {
     TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
+    TX_SDPA_OUT_F16 = 4,     /* `out` is fp16 [batch, q_heads, seq_q, d_v] instead of fp32 (the reference only has fp32
+                                output, csrc/tensor_ops.cpp:1062; halves the result's bytes) */
     TX_SDPA_P_IN_SMEM = 2    /* tensor-core kernel: stage P in shared memory instead of tensor memory
                                 (ignored for d = 512, where shared memory has no room for it) */
 };
@@ -139,13 +141,15 @@ typedef struct tx_sdpa_desc {
     const void *v;            /* [batch, kv_heads, seq_k, d_v]  dtype */
     const float *mask;        /* optional dense additive fp32 [batch, q_heads, seq_q, seq_k] */
     const int32_t *kv_lens;   /* optional [batch] on the device: keys j >= kv_lens[b] are masked */
-    float *out;               /* [batch, q_heads, seq_q, d_v] fp32 */
+    void *out;                /* [batch, q_heads, seq_q, d_v] fp32 (fp16 with TX_SDPA_OUT_F16) */
     int64_t batch, q_heads, kv_heads, seq_q, seq_k, d_k, d_v;
     int32_t dtype;            /* TX_DTYPE_* of q, k, v */
     int32_t causal;           /* nonzero: key j visible to query i iff j <= i */
     int32_t flags;            /* TX_SDPA_* */
     int32_t reserved;
     void *stream;             /* cudaStream_t; NULL = default stream */
+    float *lse;               /* optional [batch, q_heads, seq_q] fp32: log2 of sum_j 2^(score_ij * log2(e)/sqrt(d_k)),
+                                 what tx_sdpa_backward needs; tensor-core shapes only, else must be NULL */
 } tx_sdpa_desc;
 
 /* Enqueue one forward pass.  Query head h reads K/V head h / (q_heads/kv_heads). */
@@ -167,6 +171,28 @@ TX_API int64_t tx_kernel_launch_count(void);
  *      [19] wait for V, [20] wait for P, [21] PV issue.  Producer lane: [24] total, [25] wait for a
  *      free K stage, [26] wait for a free V stage. */
 TX_API int tx_profile_sections_sdpa(const tx_sdpa_desc *desc, long long *ticks32);
+
+/* ---- backward: the reference's autograd rule for 'scaled_dot_product_attention'
+ *      (tensorax/tensor.py:806-827: dV = P^T dO, dP = dO V^T, dS = P o (dP - rowsum(dP o P)) / sqrt(d),
+ *      dQ = dS K, dK = dS^T Q), which the reference evaluates with dense [Sq,Sk] temporaries through
+ *      Tensor.transpose/matmul.  Here: flash-style on the tensor cores, P rebuilt from the forward's `lse`,
+ *      gradients of grouped K/V heads summed over their query heads, no atomics (bitwise reproducible).
+ *      fp16 q/k/v with d in {64,128}, implicit masks only (causal / kv_lens); asynchronous on `stream`
+ *      (tx_sdpa_finish reports kernel-side failures).  Takes 2*batch*q_heads*seq_q*(d+2) bytes from the
+ *      device's stream-ordered pool for the fp16 copy of `dout` and the row sums, and returns them. */
+typedef struct tx_sdpa_bwd_desc {
+    const void *q, *k, *v;    /* fp16, exactly what the forward got */
+    const void *out;          /* the forward's result: fp32, or fp16 with TX_SDPA_OUT_F16 in flags */
+    const float *dout;        /* gradient of the result, fp32 [batch, q_heads, seq_q, d] */
+    const float *lse;         /* [batch, q_heads, seq_q], written by tx_sdpa_forward through desc.lse */
+    const int32_t *kv_lens;   /* optional [batch], as in the forward */
+    float *dq, *dk, *dv;      /* fp32 [batch, q_heads, seq_q, d], [batch, kv_heads, seq_k, d] x 2 */
+    int64_t batch, q_heads, kv_heads, seq_q, seq_k, d;
+    int32_t causal;
+    int32_t flags;            /* TX_SDPA_OUT_F16: dtype of `out` */
+    void *stream;
+} tx_sdpa_bwd_desc;
+TX_API int tx_sdpa_backward(const tx_sdpa_bwd_desc *desc);
 
 /* ---- host-buffer form (no reference counterpart): `desc` holds HOST pointers
  *      (q, k, v, kv_lens, out; mask must be NULL).  Copies in, runs, copies out,

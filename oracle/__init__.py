@@ -176,3 +176,56 @@ def mha_forward_f32(query, key, value, params, num_heads, mask=None):
     a = sdpa_f32(q, k, v, mask)
     merged = np.ascontiguousarray(a.transpose(0, 2, 1, 3)).reshape(B, Sq, E)
     return linear_f32(merged, params["out_weight"], params.get("out_bias"))
+
+
+# ------------------------------------------------------------------ SDPA backward (numpy, float64)
+# PARITY UNPINNED against the reference itself: its autograd rule (tensorax/tensor.py:806-827)
+# cannot run there -- `key.transpose(-2, -1)` raises ValueError for negative dims
+# (tensorax/tensor.py:963-964) and `_C.transpose_dims` is not bound -- and its tests hold no vector
+# for it.  The restatement below follows that rule line by line in float64; tests/test_oracle.py pins
+# it from the other side, against central differences of the (pinned) forward oracle.
+def _visible(Sq, Sk, causal, kv_len):
+    vis = np.ones((Sq, Sk), dtype=bool)
+    if kv_len is not None:
+        vis[:, max(int(kv_len), 0):] = False
+    if causal:
+        vis &= np.arange(Sk)[None, :] <= np.arange(Sq)[:, None]
+    return vis
+
+
+def sdpa_backward(q, k, v, dout, causal=False, kv_lens=None):
+    """(dq, dk, dv, lse2) for out = softmax(q k^T / sqrt(d) + implicit mask) v.
+
+    tensorax/tensor.py:811-827: scores = q k^T * scale (+ mask); attn = softmax(scores);
+    dv = attn^T grad; d_attn = grad v^T; dot = sum(d_attn * attn, -1);
+    d_scores = attn * (d_attn - dot) * scale; dq = d_scores k; dk = d_scores^T q.
+    Grouped K/V heads: the gradients of one K/V head are summed over its query heads.
+    lse2[b,h,i] = log2(sum_j 2^(scores_ij * log2(e))), the row statistic the device forward saves."""
+    q, k, v, dout = (np.asarray(x, dtype=np.float64) for x in (q, k, v, dout))
+    B, Hq, Sq, d = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    group = Hq // Hkv
+    scale = 1.0 / np.sqrt(np.float64(d))
+    dq = np.zeros_like(q)
+    dk = np.zeros_like(k)
+    dv = np.zeros_like(v)
+    lse2 = np.zeros((B, Hq, Sq))
+    for b in range(B):
+        vis = _visible(Sq, Sk, causal, None if kv_lens is None else kv_lens[b])
+        for h in range(Hq):
+            g = h // group
+            scores = (q[b, h] @ k[b, g].T) * scale
+            scores = np.where(vis, scores, -np.inf)
+            with np.errstate(invalid="ignore", divide="ignore"):
+                m = scores.max(axis=-1, keepdims=True)
+                e = np.exp(scores - m)
+                s = e.sum(axis=-1, keepdims=True)
+                attn = e / s
+                lse2[b, h] = ((m + np.log(s)) * np.log2(np.e))[:, 0]
+            dv[b, g] += attn.T @ dout[b, h]
+            d_attn = dout[b, h] @ v[b, g].T
+            dot = (d_attn * attn).sum(axis=-1, keepdims=True)
+            d_scores = attn * (d_attn - dot) * scale
+            dq[b, h] = d_scores @ k[b, g]
+            dk[b, g] += d_scores.T @ q[b, h]
+    return dq, dk, dv, lse2

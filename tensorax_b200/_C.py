@@ -219,7 +219,8 @@ def _validate(query, key, value, mask, who="SDPA"):
     return B, H, Hkv, Sq, Sk, dk, dv
 
 
-def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="SDPA") -> TensorImpl:
+def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="SDPA", out_dtype="float32",
+             want_lse=False):
     B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, mask, who)
     if query.device != "cuda":
         raise RuntimeError(
@@ -232,7 +233,12 @@ def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="
     f16 = query.dtype in ("float16", "half")
     # reference: output dtype string = query dtype for the generic entries; fp16 inputs give
     # float32 output exactly as scaled_dot_product_attention_mma_fp16 does
-    out = TensorImpl([B, H, Sq, dv], "float32", "cuda")
+    if out_dtype not in ("float32", "float16"):
+        raise RuntimeError(f"{who}: out_dtype must be 'float32' or 'float16'")
+    out = TensorImpl([B, H, Sq, dv], out_dtype, "cuda")
+    if out_dtype == "float16":
+        flags = int(flags) | _lib.TX_SDPA_OUT_F16
+    lse = TensorImpl([B, H, Sq], "float32", "cuda") if want_lse else None
     lens_buf = None
     if kv_lens is not None:
         lens = np.ascontiguousarray(kv_lens, dtype=np.int32)
@@ -245,11 +251,52 @@ def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="
         kv_lens=lens_buf.ptr if lens_buf is not None else None, out=out.data_ptr,
         batch=B, q_heads=H, kv_heads=Hkv, seq_q=Sq, seq_k=Sk, d_k=dk, d_v=dv,
         dtype=_lib.TX_DTYPE_F16 if f16 else _lib.TX_DTYPE_F32, causal=int(bool(causal)),
-        flags=int(flags), stream=None)
+        flags=int(flags), stream=None, lse=lse.data_ptr if lse is not None else None)
     lib = _lib.load()
     _lib.check(lib.tx_sdpa_forward(ctypes.byref(desc)))
     _lib.check(lib.tx_sdpa_finish(None))   # the reference launchers return a finished result
-    return out
+    return (out, lse) if want_lse else out
+
+
+def sdpa_backward_supported(query, key, value, mask) -> bool:
+    """Shapes the backward kernels take: float16 CUDA tensors, d_k == d_v in {64, 128}, no dense mask."""
+    return (mask is None and query.device == "cuda" and query.dtype in ("float16", "half")
+            and key.dtype == query.dtype and value.dtype == query.dtype
+            and query._shape[3] == value._shape[3] and query._shape[3] in (64, 128))
+
+
+def scaled_dot_product_attention_backward(query, key, value, out, lse, grad, causal=False, kv_lens=None):
+    """Gradients (dq, dk, dv), float32, of ``out = SDPA(query, key, value)`` for the upstream
+    gradient ``grad`` -- the reference's autograd rule, tensorax/tensor.py:806-827, which there
+    runs through dense [Sq,Sk] temporaries (and cannot run at all: Tensor.transpose rejects the
+    negative dims it is called with, tensorax/tensor.py:963-964).  ``lse`` is the row statistic
+    the forward returned with ``want_lse``."""
+    B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, None, "SDPA backward")
+    if not sdpa_backward_supported(query, key, value, None):
+        raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128} and "
+                           "implicit (causal / kv_lens) masks")
+    if list(grad._shape) != [B, H, Sq, dv] or grad.dtype != "float32" or grad.device != "cuda":
+        raise RuntimeError("SDPA backward: grad must be a float32 CUDA tensor shaped like the output")
+    if list(out._shape) != [B, H, Sq, dv] or list(lse._shape) != [B, H, Sq]:
+        raise RuntimeError("SDPA backward: out / lse do not belong to these inputs")
+    dq = TensorImpl([B, H, Sq, dk], "float32", "cuda")
+    dkk = TensorImpl([B, Hkv, Sk, dk], "float32", "cuda")
+    dvv = TensorImpl([B, Hkv, Sk, dv], "float32", "cuda")
+    lens_buf = None
+    if kv_lens is not None:
+        lens = np.ascontiguousarray(kv_lens, dtype=np.int32)
+        if lens.shape != (B,):
+            raise RuntimeError("SDPA backward: kv_lens must hold one length per batch element")
+        lens_buf = _lib.to_device(lens)
+    desc = _lib.SdpaBwdDesc(
+        q=query.data_ptr, k=key.data_ptr, v=value.data_ptr, out=out.data_ptr, dout=grad.data_ptr,
+        lse=lse.data_ptr, kv_lens=lens_buf.ptr if lens_buf is not None else None,
+        dq=dq.data_ptr, dk=dkk.data_ptr, dv=dvv.data_ptr, batch=B, q_heads=H, kv_heads=Hkv, seq_q=Sq, seq_k=Sk,
+        d=dk, causal=int(bool(causal)), flags=_lib.TX_SDPA_OUT_F16 if out.dtype == "float16" else 0, stream=None)
+    lib = _lib.load()
+    _lib.check(lib.tx_sdpa_backward(ctypes.byref(desc)))
+    _lib.check(lib.tx_sdpa_finish(None))
+    return dq, dkk, dvv
 
 
 def scaled_dot_product_attention(query, key, value, mask=None) -> TensorImpl:
@@ -306,8 +353,10 @@ def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
 
 
 def scaled_dot_product_attention_ex(query, key, value, mask=None, causal=False, kv_lens=None,
-                                    flags=0) -> TensorImpl:
+                                    flags=0, out_dtype="float32", want_lse=False):
     """No reference counterpart: implicit masks for sizes where the dense
     [B,H,Sq,Sk] mask cannot exist.  ``causal``: key j visible to query i iff
-    j <= i; ``kv_lens``: per-batch count of valid keys."""
-    return _forward(query, key, value, mask, causal=causal, kv_lens=kv_lens, flags=flags)
+    j <= i; ``kv_lens``: per-batch count of valid keys; ``out_dtype``: 'float32'
+    (what every reference entry returns) or 'float16' (half the result bytes)."""
+    return _forward(query, key, value, mask, causal=causal, kv_lens=kv_lens, flags=flags, out_dtype=out_dtype,
+                    want_lse=want_lse)

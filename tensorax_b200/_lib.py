@@ -18,6 +18,7 @@ TX_DTYPE_F32 = 0
 TX_DTYPE_F16 = 1
 TX_SDPA_FORCE_SIMT = 1
 TX_SDPA_P_IN_SMEM = 2
+TX_SDPA_OUT_F16 = 4
 
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (
@@ -30,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "tx_cast_f32_to_f16_cuda", "tx_repeat_interleave_cuda", "tx_linear_f32_cuda", "tx_linear_set_cuda_cores_only",
     "tx_sdpa_forward", "tx_sdpa_finish", "tx_sdpa_uses_tensor_cores",
     "tx_kernel_launch_count", "tx_profile_sections_sdpa", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
+    "tx_sdpa_backward",
 )
 
 
@@ -41,7 +43,18 @@ class SdpaDesc(ctypes.Structure):
         ("batch", c_int64), ("q_heads", c_int64), ("kv_heads", c_int64),
         ("seq_q", c_int64), ("seq_k", c_int64), ("d_k", c_int64), ("d_v", c_int64),
         ("dtype", c_int32), ("causal", c_int32), ("flags", c_int32), ("reserved", c_int32),
-        ("stream", c_void_p),
+        ("stream", c_void_p), ("lse", c_void_p),
+    ]
+
+
+class SdpaBwdDesc(ctypes.Structure):
+    """Mirror of ``tx_sdpa_bwd_desc``."""
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("dout", c_void_p),
+        ("lse", c_void_p), ("kv_lens", c_void_p), ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p),
+        ("batch", c_int64), ("q_heads", c_int64), ("kv_heads", c_int64),
+        ("seq_q", c_int64), ("seq_k", c_int64), ("d", c_int64),
+        ("causal", c_int32), ("flags", c_int32), ("stream", c_void_p),
     ]
 
 
@@ -88,6 +101,7 @@ def load():
     lib.tx_sdpa_forward.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]
+    lib.tx_sdpa_backward.argtypes = [ctypes.POINTER(SdpaBwdDesc)]
     lib.tx_sdpa_uses_tensor_cores.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_finish.argtypes = [c_void_p]
     lib.tx_sdpa_fp16_static_scratch.argtypes = [c_void_p] * 4 + [c_int64] * 6 + [c_int32, c_void_p, c_void_p]

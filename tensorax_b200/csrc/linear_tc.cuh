@@ -174,8 +174,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 const int quarter = warp & 3;
                 const int row = s0 + quarter * 32 + lane;
                 const uint32_t t_acc = tmem + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
                 const int n_main = k_tiles < 3 ? k_tiles : 3;      // main accumulators that were written
+#pragma unroll 1
                 for (int c = 0; c < LTC_BN / 32; ++c) {
                     uint32_t v[32];
                     ptx::tmem_ld32(t_acc + 384 + c * 32, v);            // corrections first, then the main sums

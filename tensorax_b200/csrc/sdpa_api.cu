@@ -21,6 +21,7 @@
 #include "linear_tc.cuh"
 #include "sdpa_simt.cuh"
 #include "sdpa_tc.cuh"
+#include "sdpa_bwd.cuh"
 
 namespace {
 
@@ -131,6 +132,8 @@ int make_map_f32(CUtensorMap *m, const void *base, int rank, const cuuint64_t *d
 }
 
 // ------------------------------------------------------------------ validation
+bool tc_eligible(const tx_sdpa_desc *d);
+
 int validate(const tx_sdpa_desc *d)
 {
     if (!d) return fail(TX_ERR_INVALID, "SDPA: null descriptor");
@@ -146,6 +149,9 @@ int validate(const tx_sdpa_desc *d)
         return fail(TX_ERR_INVALID, "SDPA: dtype must be float32 or float16");
     if (d->batch * d->q_heads > 0x7fffffffLL / 2 || d->seq_q > 0x3fffffffLL || d->seq_k > 0x3fffffffLL)
         return fail(TX_ERR_UNSUPPORTED, "SDPA: dimension too large");
+    if (d->lse && !tc_eligible(d))
+        return fail(TX_ERR_UNSUPPORTED, "SDPA: the log-sum-exp output is written by the tensor-core kernel only "
+                                        "(fp16, no dense mask, d_k == d_v in {64,128,256,512})");
     return TX_OK;
 }
 
@@ -197,6 +203,8 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, d->d_v, Cfg::BN)) return rc;
     txb::TcParams p;
     p.out = d->out;
+    p.out_f16 = (d->flags & TX_SDPA_OUT_F16) ? 1 : 0;
+    p.lse = d->lse;
     p.kv_lens = d->kv_lens;
     p.status = status;
     p.Hq = (int)d->q_heads;
@@ -243,6 +251,48 @@ int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
 }
 
+template <int D>
+int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __half *dout_h, const float *delta)
+{
+    using DqCfg = txb::BwdDqCfg<D, 64, 2>;
+    using DkvCfg = txb::BwdDkvCfg<D, 64, 2>;
+    txb::BwdParams p;
+    p.lse = d->lse; p.delta = delta; p.kv_lens = d->kv_lens;
+    p.dq = d->dq; p.dk = d->dk; p.dv = d->dv;
+    p.status = status;
+    p.Hq = (int)d->q_heads; p.Hkv = (int)d->kv_heads; p.Sq = (int)d->seq_q; p.Sk = (int)d->seq_k;
+    p.causal = d->causal ? 1 : 0;
+    p.scale = 1.0f / std::sqrt((float)D);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    {
+        CUtensorMap tq, tdo, tk, tv;
+        if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, D, DqCfg::BM)) return rc;
+        if (int rc = make_map(&tdo, dout_h, d->batch * d->q_heads, d->seq_q, D, DqCfg::BM)) return rc;
+        if (int rc = make_map(&tk, d->k, d->batch * d->kv_heads, d->seq_k, D, DqCfg::BN)) return rc;
+        if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, D, DqCfg::BN)) return rc;
+        TX_CUDA(cudaFuncSetAttribute(txb::sdpa_bwd_dq_kernel<DqCfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)DqCfg::SMEM_BYTES));
+        dim3 grid((unsigned)((d->seq_q + DqCfg::BM - 1) / DqCfg::BM), (unsigned)(d->batch * d->q_heads));
+        txb::sdpa_bwd_dq_kernel<DqCfg><<<grid, DqCfg::THREADS, DqCfg::SMEM_BYTES, st>>>(tq, tdo, tk, tv, p);
+        g_launches++;
+        TX_CUDA(cudaGetLastError());
+    }
+    {
+        CUtensorMap tq, tdo, tk, tv;
+        if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, D, DkvCfg::BQ)) return rc;
+        if (int rc = make_map(&tdo, dout_h, d->batch * d->q_heads, d->seq_q, D, DkvCfg::BQ)) return rc;
+        if (int rc = make_map(&tk, d->k, d->batch * d->kv_heads, d->seq_k, D, DkvCfg::BMK)) return rc;
+        if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, D, DkvCfg::BMK)) return rc;
+        TX_CUDA(cudaFuncSetAttribute(txb::sdpa_bwd_dkv_kernel<DkvCfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)DkvCfg::SMEM_BYTES));
+        dim3 grid((unsigned)((d->seq_k + DkvCfg::BMK - 1) / DkvCfg::BMK), (unsigned)(d->batch * d->kv_heads));
+        txb::sdpa_bwd_dkv_kernel<DkvCfg><<<grid, DkvCfg::THREADS, DkvCfg::SMEM_BYTES, st>>>(tq, tdo, tk, tv, p);
+        g_launches++;
+        TX_CUDA(cudaGetLastError());
+    }
+    return TX_OK;
+}
+
 int forward(const tx_sdpa_desc *d)
 {
     if (int rc = validate(d)) return rc;
@@ -258,6 +308,7 @@ int forward(const tx_sdpa_desc *d)
     p.mask = d->mask;
     p.kv_lens = d->kv_lens;
     p.out = d->out;
+    p.out_f16 = (d->flags & TX_SDPA_OUT_F16) ? 1 : 0;
     p.B = d->batch; p.Hq = d->q_heads; p.Hkv = d->kv_heads;
     p.Sq = d->seq_q; p.Sk = d->seq_k; p.dk = d->d_k; p.dv = d->d_v;
     p.causal = d->causal ? 1 : 0;
@@ -703,6 +754,48 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     return rc;
 }
 
+int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)
+{
+    if (!d) return fail(TX_ERR_INVALID, "SDPA backward: null descriptor");
+    if (!d->q || !d->k || !d->v || !d->out || !d->dout || !d->lse || !d->dq || !d->dk || !d->dv)
+        return fail(TX_ERR_INVALID, "SDPA backward: q, k, v, out, dout, lse, dq, dk, dv must not be null");
+    if (d->batch <= 0 || d->q_heads <= 0 || d->kv_heads <= 0 || d->seq_q <= 0 || d->seq_k <= 0)
+        return fail(TX_ERR_INVALID, "SDPA backward: every dimension must be positive");
+    if (d->q_heads % d->kv_heads != 0)
+        return fail(TX_ERR_INVALID, "SDPA backward: q_heads %lld not a multiple of kv_heads %lld",
+                    (long long)d->q_heads, (long long)d->kv_heads);
+    if (d->d != 64 && d->d != 128)
+        return fail(TX_ERR_UNSUPPORTED, "SDPA backward: built for d in {64, 128}, got %lld", (long long)d->d);
+    if (d->batch * d->q_heads > 65535 || d->seq_q > 0x3fffffffLL || d->seq_k > 0x3fffffffLL)
+        return fail(TX_ERR_UNSUPPORTED, "SDPA backward: dimension too large");
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al(d->q) || !al(d->k) || !al(d->v) || !al(d->out) || !al(d->dout) || !al(d->dq) || !al(d->dk) || !al(d->dv))
+        return fail(TX_ERR_INVALID, "SDPA backward: pointers must be 16-byte aligned");
+    if (int rc = ensure_device()) return rc;
+    int *status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(d->stream);
+    const int64_t rows = d->batch * d->q_heads * d->seq_q;
+    const size_t h_bytes = align_up((size_t)rows * (size_t)d->d * 2, 256);
+    char *ws = nullptr;
+    TX_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&ws), h_bytes + (size_t)rows * 4, st));
+    __half *dout_h = reinterpret_cast<__half *>(ws);
+    float *delta = reinterpret_cast<float *>(ws + h_bytes);
+    const int warps = 8;
+    const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
+    if (d->flags & TX_SDPA_OUT_F16)
+        txb::sdpa_bwd_prep_kernel<__half><<<blocks, warps * 32, 0, st>>>(d->dout, static_cast<const __half *>(d->out),
+                                                                       dout_h, delta, rows, (int)d->d);
+    else
+        txb::sdpa_bwd_prep_kernel<float><<<blocks, warps * 32, 0, st>>>(d->dout, static_cast<const float *>(d->out),
+                                                                      dout_h, delta, rows, (int)d->d);
+    g_launches++;
+    int rc = (cudaGetLastError() == cudaSuccess) ? TX_OK : fail(TX_ERR_CUDA, "SDPA backward: preprocess launch failed");
+    if (rc == TX_OK) rc = d->d == 64 ? launch_bwd<64>(d, st, status, dout_h, delta) : launch_bwd<128>(d, st, status, dout_h, delta);
+    (void)cudaFreeAsync(ws, st);        // ordered after the kernels on `st`
+    return rc;
+}
+
 int tx_sdpa_finish(void *stream) { return finish(static_cast<cudaStream_t>(stream)); }
 
 int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc)
@@ -717,6 +810,7 @@ int tx_sdpa_forward_host(const tx_sdpa_desc *h)
 {
     if (int rc = validate(h)) return rc;
     if (h->mask) return fail(TX_ERR_UNSUPPORTED, "SDPA host form: dense masks are not taken; use causal / kv_lens");
+    if (h->lse) return fail(TX_ERR_UNSUPPORTED, "SDPA host form: no log-sum-exp output");
     if (int rc = ensure_device()) return rc;
     // The call is cut into chunks of whole (batch, K/V head) units -- contiguous slabs of Q, K, V and
     // O -- so that the upload of chunk i+1, the kernel of chunk i and the download of chunk i-1 run
@@ -727,7 +821,7 @@ int tx_sdpa_forward_host(const tx_sdpa_desc *h)
     const size_t uq = (size_t)(group * h->seq_q * h->d_k) * es;       // bytes of one unit
     const size_t uk = (size_t)(h->seq_k * h->d_k) * es;
     const size_t uv = (size_t)(h->seq_k * h->d_v) * es;
-    const size_t uo = (size_t)(group * h->seq_q * h->d_v) * 4;
+    const size_t uo = (size_t)(group * h->seq_q * h->d_v) * ((h->flags & TX_SDPA_OUT_F16) ? 2 : 4);
     const size_t nl = h->kv_lens ? (size_t)units * 4 : 0;
     const size_t oq = 0, ok = align_up(oq + uq * units, 256), ov = align_up(ok + uk * units, 256),
                  oo = align_up(ov + uv * units, 256), ol = align_up(oo + uo * units, 256);
@@ -763,7 +857,7 @@ int tx_sdpa_forward_host(const tx_sdpa_desc *h)
         TX_CUDA(cudaStreamWaitEvent(st, hp->in_done[c], 0));
         tx_sdpa_desc d = *h;                       // the chunk as a problem of its own: one K/V head per "batch"
         d.q = w + oq + uq * u0; d.k = w + ok + uk * u0; d.v = w + ov + uv * u0;
-        d.out = reinterpret_cast<float *>(w + oo + uo * u0);
+        d.out = w + oo + uo * u0;
         d.kv_lens = nl ? reinterpret_cast<const int32_t *>(w + ol) + u0 : nullptr;
         d.batch = nu; d.q_heads = group; d.kv_heads = 1;
         if (int rc = forward(&d)) return rc;

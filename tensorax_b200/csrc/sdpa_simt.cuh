@@ -32,9 +32,10 @@ struct SimtParams {
     const void *q, *k, *v;   // [B,Hq,Sq,dk], [B,Hkv,Sk,dk], [B,Hkv,Sk,dv]
     const float *mask;       // optional dense additive [B,Hq,Sq,Sk]
     const int32_t *kv_lens;  // optional [B]
-    float *out;              // [B,Hq,Sq,dv] fp32
+    void *out;               // [B,Hq,Sq,dv] fp32, or fp16 when out_f16
     int64_t B, Hq, Hkv, Sq, Sk, dk, dv;
     int causal;
+    int out_f16;
     float scale;
 };
 
@@ -187,7 +188,12 @@ sdpa_simt_kernel(const SimtParams p)
 #pragma unroll
         for (int c = 0; c < DVC; ++c) {
             const int64_t col = dv0 + lane + 32 * c;
-            if (col < p.dv) p.out[(bh * p.Sq + row) * p.dv + col] = o[r][c] / l;   // l == 0 -> NaN, as the reference
+            if (col < p.dv) {
+                const float val = o[r][c] / l;                                    // l == 0 -> NaN, as the reference
+                const int64_t idx = (bh * p.Sq + row) * p.dv + col;
+                if (p.out_f16) static_cast<__half *>(p.out)[idx] = __float2half_rn(val);
+                else static_cast<float *>(p.out)[idx] = val;
+            }
         }
     }
 }

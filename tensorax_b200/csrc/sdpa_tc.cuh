@@ -41,12 +41,14 @@
 namespace txb {
 
 struct TcParams {
-    float *out;               // [B,Hq,Sq,dv_total] fp32
+    void *out;                // [B,Hq,Sq,dv_total] fp32, or fp16 when out_f16
+    float *lse;               // optional [B,Hq,Sq]: log2 of the row's sum of 2^(score*scale_log2)
     const int32_t *kv_lens;   // optional [B]
     int *status;              // device word: 0 = ok, else first failing wait's code
     int Hq, Hkv, Sq, Sk;
     int dv_total;             // row length of `out` (= DV * gridDim.z)
     int causal;
+    int out_f16;
     float scale_log2;         // (1/sqrt(d_k)) * log2(e)
     long long *prof;          // optional [32] cycle counters written by CTA (0,0,0) (section profile)
 };
@@ -577,7 +579,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (ok) {
                 ptx::tc_fence_after_sync();
                 const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
-                float *orow = p.out + ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
+                const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
+                float *orow = static_cast<float *>(p.out) + obase;
+                __half *orow_h = static_cast<__half *>(p.out) + obase;
+                if (p.lse && dv0 == 0 && row < p.Sq) p.lse[(size_t)bh * p.Sq + row] = m_used + __log2f(l);
 #pragma unroll
                 for (int c = 0; c < DV / 32; ++c) {
                     uint32_t o[32];
@@ -585,14 +590,26 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ptx::tmem_wait_ld();
                     ptx::reg_fence32(o);
                     if (row < p.Sq) {
+                        if (p.out_f16) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            float4 f;
-                            f.x = __uint_as_float(o[i]) * inv_l;
-                            f.y = __uint_as_float(o[i + 1]) * inv_l;
-                            f.z = __uint_as_float(o[i + 2]) * inv_l;
-                            f.w = __uint_as_float(o[i + 3]) * inv_l;
-                            *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 h;
+                                h.x = ptx::pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                                h.y = ptx::pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                                h.z = ptx::pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                                h.w = ptx::pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                                *reinterpret_cast<uint4 *>(orow_h + c * 32 + i) = h;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 f;
+                                f.x = __uint_as_float(o[i]) * inv_l;
+                                f.y = __uint_as_float(o[i + 1]) * inv_l;
+                                f.z = __uint_as_float(o[i + 2]) * inv_l;
+                                f.w = __uint_as_float(o[i + 3]) * inv_l;
+                                *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
+                            }
                         }
                     }
                 }
@@ -609,8 +626,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         if (!run && *abort_flag == 0 && row < p.Sq) {
             // no visible key at all for this tile: the reference's 0/0
-            float *orow = p.out + ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
-            for (int i = 0; i < DV; ++i) orow[i] = __int_as_float(0x7fc00000);
+            const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
+            if (p.out_f16) {
+                __half *orow_h = static_cast<__half *>(p.out) + obase;
+                for (int i = 0; i < DV; ++i) orow_h[i] = __ushort_as_half((unsigned short)0x7e00);
+            } else {
+                float *orow = static_cast<float *>(p.out) + obase;
+                for (int i = 0; i < DV; ++i) orow[i] = __int_as_float(0x7fc00000);
+            }
+            if (p.lse && dv0 == 0) p.lse[(size_t)bh * p.Sq + row] = __int_as_float(0x7fc00000);
         }
     }
 

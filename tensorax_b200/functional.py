@@ -54,11 +54,25 @@ def scaled_dot_product_attention(query: Tensor, key: Tensor, value: Tensor,
     _check(query, key, value, mask, _MSG4D)
     if not _C:
         raise RuntimeError("C++ backend not available. Please build the package first.")
-    c = _C.scaled_dot_product_attention(query._c_tensor, key._c_tensor, value._c_tensor,
-                                        mask._c_tensor if mask is not None else None)
-    if query.requires_grad or key.requires_grad or value.requires_grad:
+    needs_grad = query.requires_grad or key.requires_grad or value.requires_grad
+    mask_c = mask._c_tensor if mask is not None else None
+    if needs_grad and _C.sdpa_backward_supported(query._c_tensor, key._c_tensor, value._c_tensor, mask_c):
+        return _with_saved_stats(query, key, value, mask, False, None, "float32")
+    c = _C.scaled_dot_product_attention(query._c_tensor, key._c_tensor, value._c_tensor, mask_c)
+    if needs_grad:
+        # same autograd tuple as the reference (tensorax/functional.py:314-316); backward() of this
+        # result raises, because only the float16 tensor-core shapes have a backward kernel
         return _result(c, True, ("scaled_dot_product_attention", query, key, value, mask))
     return _result(c)
+
+
+def _with_saved_stats(query, key, value, mask, causal, kv_lens, out_dtype) -> Tensor:
+    """Forward that also keeps the per-row log-sum-exp, so that Tensor.backward can rebuild P."""
+    c, lse = _C.scaled_dot_product_attention_ex(query._c_tensor, key._c_tensor, value._c_tensor, None,
+                                                causal=causal, kv_lens=kv_lens, out_dtype=out_dtype, want_lse=True)
+    out = _result(c, True, ("scaled_dot_product_attention", query, key, value, mask))
+    out._saved = {"lse": lse, "causal": bool(causal), "kv_lens": None if kv_lens is None else list(kv_lens)}
+    return out
 
 
 def _sdpa_variant(query, key, value, mask, backend_name: str) -> Tensor:
@@ -112,14 +126,23 @@ def scaled_dot_product_attention_mma_fp16(query: Tensor, key: Tensor, value: Ten
 
 def scaled_dot_product_attention_ex(query: Tensor, key: Tensor, value: Tensor,
                                     mask: Optional[Tensor] = None, causal: bool = False,
-                                    kv_lens: Optional[Sequence[int]] = None) -> Tensor:
+                                    kv_lens: Optional[Sequence[int]] = None,
+                                    out_dtype: str = "float32") -> Tensor:
     """No reference counterpart.  Implicit masks for shapes where the reference's
     dense [B,H,Sq,Sk] masks cannot be built: ``causal`` (key j visible to query i
     iff j <= i, what create_causal_mask encodes) and ``kv_lens`` (per-batch valid
-    key count, what create_padding_mask encodes).  K/V may have fewer heads than Q."""
+    key count, what create_padding_mask encodes).  K/V may have fewer heads than Q.
+    ``out_dtype='float16'`` returns a float16 tensor (the reference's fp16 entry always
+    returns float32, tensorax/functional.py:397)."""
     _check(query, key, value, mask, _MSG4D)
     if not _C:
         raise RuntimeError("C++ backend not available.")
-    return _result(_C.scaled_dot_product_attention_ex(
-        query._c_tensor, key._c_tensor, value._c_tensor,
-        mask._c_tensor if mask is not None else None, causal=causal, kv_lens=kv_lens))
+    mask_c = mask._c_tensor if mask is not None else None
+    needs_grad = query.requires_grad or key.requires_grad or value.requires_grad
+    if needs_grad and _C.sdpa_backward_supported(query._c_tensor, key._c_tensor, value._c_tensor, mask_c):
+        return _with_saved_stats(query, key, value, mask, causal, kv_lens, out_dtype)
+    c = _C.scaled_dot_product_attention_ex(query._c_tensor, key._c_tensor, value._c_tensor, mask_c, causal=causal,
+                                           kv_lens=kv_lens, out_dtype=out_dtype)
+    if needs_grad:
+        return _result(c, True, ("scaled_dot_product_attention", query, key, value, mask))
+    return _result(c)

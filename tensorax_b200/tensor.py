@@ -120,5 +120,40 @@ class Tensor:
         """tensorax/tensor.py:933-959."""
         return Tensor._wrap(_C.repeat_interleave(self._c_tensor, int(repeats), int(dim)))
 
+    def backward(self, grad: Optional["Tensor"] = None) -> None:
+        """Backpropagation entry of the reference (tensorax/tensor.py:604-620) for the one
+        operation this package records: 'scaled_dot_product_attention' (tensorax/tensor.py:806-827),
+        evaluated by the flash backward kernels instead of dense [Sq,Sk] temporaries.  A tensor that
+        already holds a gradient would need tensor addition to accumulate, which is outside this
+        package: that raises instead of silently overwriting."""
+        if not self.requires_grad:
+            return
+        if grad is None:
+            if self.size != 1:
+                raise RuntimeError("grad must be specified for non-scalar tensors")
+            grad = Tensor(np.ones(self._shape, dtype=np.float32), device=self.device)
+        if self.grad is not None:
+            raise RuntimeError("gradient accumulation is not available in tensorax_b200: clear .grad first")
+        self.grad = grad
+        if self._grad_fn is None:
+            return
+        op, *inputs = self._grad_fn
+        if op != "scaled_dot_product_attention":
+            raise RuntimeError(f"backward of {op!r} is outside tensorax_b200")
+        query, key, value = inputs[0], inputs[1], inputs[2]
+        saved = getattr(self, "_saved", None)
+        if saved is None:
+            raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128} and "
+                               "implicit (causal / kv_lens) masks; this forward kept no row statistics")
+        g = grad if grad.dtype == "float32" else None
+        if g is None or g.device != "cuda":
+            raise RuntimeError("SDPA backward: grad must be a float32 CUDA tensor")
+        dq, dk, dv = _C.scaled_dot_product_attention_backward(
+            query._c_tensor, key._c_tensor, value._c_tensor, self._c_tensor, saved["lse"], g._c_tensor,
+            causal=saved["causal"], kv_lens=saved["kv_lens"])
+        for t, c in ((query, dq), (key, dk), (value, dv)):
+            if t.requires_grad:
+                t.backward(Tensor._wrap(c))
+
     def __repr__(self) -> str:
         return f"Tensor(shape={self.shape}, dtype={self.dtype}, device={self.device})"

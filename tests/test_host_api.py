@@ -33,8 +33,11 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_desc_struct_layout_matches_header():
-    # 6 pointers + 7 int64 + 4 int32 + 1 pointer, no padding surprises
-    assert ctypes.sizeof(_lib.SdpaDesc) == 6 * 8 + 7 * 8 + 4 * 4 + 8
+    # 6 pointers + 7 int64 + 4 int32 + 2 pointers, no padding surprises
+    assert ctypes.sizeof(_lib.SdpaDesc) == 6 * 8 + 7 * 8 + 4 * 4 + 2 * 8
+    assert _lib.SdpaDesc.lse.offset == 6 * 8 + 7 * 8 + 4 * 4 + 8
+    # backward: 10 pointers + 6 int64 + 2 int32 + 1 pointer
+    assert ctypes.sizeof(_lib.SdpaBwdDesc) == 10 * 8 + 6 * 8 + 2 * 4 + 8
 
 
 @pytest.mark.skipif(_lib.cuda_is_available(), reason="checks the no-device behaviour")
@@ -48,6 +51,31 @@ def test_no_device_means_loud_failure_not_fallback():
     q = ts.Tensor.randn((1, 1, 2, 2))
     with pytest.raises(RuntimeError, match="CUDA path only"):
         F.scaled_dot_product_attention(q, q, q)
+
+
+def test_backward_rejects_bad_descriptors_before_any_launch():
+    lib = _lib.load()
+    assert lib.tx_sdpa_backward(None) == 1
+    d = _lib.SdpaBwdDesc(q=16, k=16, v=16, out=16, dout=16, lse=16, dq=16, dk=16, dv=16, batch=1, q_heads=2,
+                         kv_heads=2, seq_q=8, seq_k=8, d=32)
+    assert lib.tx_sdpa_backward(ctypes.byref(d)) == 5 and b"d in {64, 128}" in lib.tx_last_error()
+    d.d = 64
+    d.kv_heads = 3
+    assert lib.tx_sdpa_backward(ctypes.byref(d)) == 1
+    d.kv_heads = 2
+    d.lse = None
+    assert lib.tx_sdpa_backward(ctypes.byref(d)) == 1 and b"must not be null" in lib.tx_last_error()
+
+
+def test_backward_of_unsupported_forward_raises():
+    """A result recorded for autograd whose shapes have no backward kernel fails loudly."""
+    t = ts.Tensor.__new__(ts.Tensor)
+    t.requires_grad, t.grad, t._grad_fn, t._shape, t._size = True, None, ("scaled_dot_product_attention", t, t, t, None), (2,), 2
+    with pytest.raises(RuntimeError, match="grad must be specified"):
+        t.backward()
+    g = ts.Tensor.randn((2,))
+    with pytest.raises(RuntimeError, match="kept no row statistics"):
+        t.backward(g)
 
 
 def test_invalid_arguments_are_rejected_before_any_launch():

@@ -114,3 +114,52 @@ def test_linear_and_mha_forward_restatements(golden):
                                                "q_bias", "k_bias", "v_bias", "out_bias")}
     out = oracle.mha_forward_f32(golden["mha_xq"], golden["mha_xk"], golden["mha_xv"], params, num_heads=4)
     assert bit_equal(out, golden["mha_out"])
+
+
+# ------------------------------------------------------------------ backward oracle
+@pytest.mark.parametrize("causal,lens,hkv", [(False, None, 2), (True, None, 1), (True, [9, 5], 2), (False, [4, 11], 1)])
+def test_backward_oracle_matches_central_differences_of_the_forward_oracle(causal, lens, hkv):
+    """The backward restatement (tensorax/tensor.py:806-827) is the gradient of the pinned forward
+    oracle: d/dx sum(out * g) by central differences, every input element of small tensors."""
+    rng = np.random.default_rng(7)
+    B, Hq, Sq, Sk, d = 2, 2, 6, 11, 4
+    q = rng.standard_normal((B, Hq, Sq, d))
+    k = rng.standard_normal((B, hkv, Sk, d))
+    v = rng.standard_normal((B, hkv, Sk, d))
+    g = rng.standard_normal((B, Hq, Sq, d))
+    dq, dk, dv, lse2 = oracle.sdpa_backward(q, k, v, g, causal=causal, kv_lens=lens)
+
+    def loss(q_, k_, v_):
+        # float64 forward with the same masks; checked against the C oracle below
+        out = np.zeros((B, Hq, Sq, d))
+        for b in range(B):
+            vis = oracle._visible(Sq, Sk, causal, None if lens is None else lens[b])
+            for h in range(Hq):
+                s = np.where(vis, (q_[b, h] @ k_[b, h // (Hq // hkv)].T) / np.sqrt(d), -np.inf)
+                p = np.exp(s - s.max(-1, keepdims=True))
+                out[b, h] = (p / p.sum(-1, keepdims=True)) @ v_[b, h // (Hq // hkv)]
+        return out
+
+    ref_out = oracle.sdpa_structured(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32),
+                                     causal=causal, kv_lens=lens)
+    np.testing.assert_allclose(loss(q, k, v), ref_out, atol=2e-6)
+    eps = 1e-5
+    for name, x, gx in (("q", q, dq), ("k", k, dk), ("v", v, dv)):
+        num = np.zeros_like(x)
+        it = np.nditer(x, flags=["multi_index"])
+        for _ in it:
+            i = it.multi_index
+            old = x[i]
+            x[i] = old + eps
+            up = (loss(q, k, v) * g).sum()
+            x[i] = old - eps
+            dn = (loss(q, k, v) * g).sum()
+            x[i] = old
+            num[i] = (up - dn) / (2 * eps)
+        np.testing.assert_allclose(gx, num, atol=1e-7, rtol=1e-6, err_msg=name)
+    # the saved row statistic reproduces the probabilities
+    s2 = np.einsum("bhid,bhjd->bhij", q, np.repeat(k, Hq // hkv, axis=1)) / np.sqrt(d) * np.log2(np.e)
+    p = np.exp2(s2 - lse2[..., None])
+    for b in range(B):
+        vis = oracle._visible(Sq, Sk, causal, None if lens is None else lens[b])
+        np.testing.assert_allclose((p[b] * vis).sum(-1), 1.0, rtol=1e-12)
