@@ -73,10 +73,12 @@ __global__ void sdpa_bwd_prep_kernel(const float *__restrict__ dout, const OT *_
 }
 
 // ------------------------------------------------------------------ dQ
-template <int D_, int BN_, int NS_>
+// WGS: row warpgroups (4 warps, one thread per TMEM lane each); with 2, each takes half of a tile's columns.
+template <int D_, int BN_, int NS_, int WGS_ = 1>
 struct BwdDqCfg {
-    static constexpr int D = D_, BN = BN_, NS = NS_, BM = 128;
-    static constexpr int THREADS = 192;
+    static constexpr int D = D_, BN = BN_, NS = NS_, BM = 128, WGS = WGS_;
+    static constexpr int CW = BN / WGS;                      // tile columns per warpgroup
+    static constexpr int THREADS = 64 + 128 * WGS;
     static constexpr int KP = D / 64;
     static constexpr uint32_t Q_BYTES = BM * D * 2;          // Q tile, dO tile
     static constexpr uint32_t KV_BYTES = BN * D * 2;         // one K or V stage
@@ -93,7 +95,8 @@ struct BwdDqCfg {
     static constexpr uint32_t COLS_USED = 2 * BN + D + BN / 2;
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
-    static_assert(D % 64 == 0 && BN % 32 == 0 && COLS_USED <= 512 && SMEM_BYTES <= 232448, "tile shape");
+    static_assert(D % 64 == 0 && CW % 32 == 0 && (D / 32) % WGS == 0 && COLS_USED <= 512 && SMEM_BYTES <= 232448,
+                  "tile shape");
 };
 
 template <class Cfg>
@@ -132,8 +135,8 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ptx::mbar_init(qdo_full, 1);
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(dp_full, 1);
-        ptx::mbar_init(s_free, 4);
-        ptx::mbar_init(ds_full, 4);
+        ptx::mbar_init(s_free, 4 * Cfg::WGS);
+        ptx::mbar_init(ds_full, 4 * Cfg::WGS);
         ptx::mbar_init(dq_done, 1);
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(k_full + 8 * s, 1);
@@ -272,12 +275,15 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, BWD_ERR_MMA); }
         }
     } else {
+        constexpr int CW = Cfg::CW;
         const int quarter = warp & 3;
+        const int wg = (warp - 2) >> 2;
+        const int c0 = wg * CW;                     // this warpgroup's first column of every tile
         const int r = quarter * 32 + lane;
         const int row = q0 + r;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const uint32_t t_s = tmem + lane_base + Cfg::COL_S, t_dp = tmem + lane_base + Cfg::COL_DP,
-                       t_dq = tmem + lane_base + Cfg::COL_DQ, t_ds = tmem + lane_base + Cfg::COL_DS;
+        const uint32_t t_s = tmem + lane_base + Cfg::COL_S + c0, t_dp = tmem + lane_base + Cfg::COL_DP + c0,
+                       t_dq = tmem + lane_base + Cfg::COL_DQ, t_ds = tmem + lane_base + Cfg::COL_DS + c0 / 2;
         const bool row_ok = row < p.Sq;
         // a row outside the problem gets lse = +inf: every P of it is 2^(-inf) = 0
         const float lse = row_ok ? p.lse[(size_t)bh * p.Sq + row] : INFINITY;
@@ -289,30 +295,30 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (lane == 0) ptx::mbar_arrive(bar);
         };
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int kv0 = j * BN;
+            const int kv0 = j * BN + c0;
             ok = ptx::mbar_wait(s_full, (uint32_t)j & 1u, abort_flag);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            uint32_t sv[BN], dpv[BN];
-            ptx::tmem_ld_cols<BN>(t_s, sv);
+            uint32_t sv[CW], dpv[CW];
+            ptx::tmem_ld_cols<CW>(t_s, sv);
             ok = ptx::mbar_wait(dp_full, (uint32_t)j & 1u, abort_flag);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            ptx::tmem_ld_cols<BN>(t_dp, dpv);
+            ptx::tmem_ld_cols<CW>(t_dp, dpv);
             ptx::tmem_wait_ld();
-            ptx::reg_fence_cols<BN>(sv);
-            ptx::reg_fence_cols<BN>(dpv);
+            ptx::reg_fence_cols<CW>(sv);
+            ptx::reg_fence_cols<CW>(dpv);
             arrive_warp(s_free);
-            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0));
-            uint32_t pk[BN / 2];
+            const bool need_mask = (kv0 + CW > kv_limit) || (p.causal && (kv0 + CW - 1 > q0));
+            uint32_t pk[CW / 2];
 #pragma unroll
-            for (int i = 0; i < BN; i += 2) {
+            for (int i = 0; i < CW; i += 2) {
                 float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse));
                 float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse));
                 if (need_mask) {
-                    const int c0 = kv0 + i, c1 = c0 + 1;
-                    if (!(c0 < kv_limit && (!p.causal || c0 <= row))) p0 = 0.f;
-                    if (!(c1 < kv_limit && (!p.causal || c1 <= row))) p1 = 0.f;
+                    const int k0 = kv0 + i, k1 = k0 + 1;
+                    if (!(k0 < kv_limit && (!p.causal || k0 <= row))) p0 = 0.f;
+                    if (!(k1 < kv_limit && (!p.causal || k1 <= row))) p1 = 0.f;
                 }
                 const float d0 = p0 * (__uint_as_float(dpv[i]) - delta) * p.scale;
                 const float d1 = p1 * (__uint_as_float(dpv[i + 1]) - delta) * p.scale;
@@ -323,7 +329,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
             }
-            ptx::tmem_st_cols<BN / 2>(t_ds, pk);
+            ptx::tmem_st_cols<CW / 2>(t_ds, pk);
             ptx::tmem_wait_st();
             arrive_warp(ds_full);
         }
@@ -333,7 +339,8 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 ptx::tc_fence_after_sync();
                 float *grow = p.dq + ((size_t)bh * p.Sq + row) * D;
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int cc = 0; cc < D / 32 / Cfg::WGS; ++cc) {
+                    const int c = cc * Cfg::WGS + wg;          // the warpgroups share the row's chunks
                     uint32_t o[32];
                     ptx::tmem_ld32(t_dq + c * 32, o);
                     ptx::tmem_wait_ld();
@@ -369,16 +376,22 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }
 
 // ------------------------------------------------------------------ dK, dV
-template <int D_, int BQ_, int NS_>
+// PS_SMEM: P^T and dS^T are staged in shared memory (SS-form MMAs) instead of tensor memory, which
+// brings the CTA down to 256 tensor-memory columns at d = 64 so that two CTAs share an SM.
+template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false>
 struct BwdDkvCfg {
-    static constexpr int D = D_, BQ = BQ_, NS = NS_, BMK = 128;
-    static constexpr int THREADS = 192;
+    static constexpr int D = D_, BQ = BQ_, NS = NS_, BMK = 128, WGS = WGS_;
+    static constexpr bool PS_SMEM = PS_SMEM_;
+    static constexpr int CW = BQ / WGS;                      // tile columns (queries) per warpgroup
+    static constexpr int THREADS = 64 + 128 * WGS;
     static constexpr int KP = D / 64;
     static constexpr uint32_t KV_BYTES = BMK * D * 2;        // resident K tile, V tile
     static constexpr uint32_t Q_BYTES = BQ * D * 2;          // one Q or dO stage
     static constexpr uint32_t Q_PANEL = BQ * 128;
     static constexpr uint32_t OFF_K = 0, OFF_V = KV_BYTES, OFF_Q = 2 * KV_BYTES, OFF_DO = OFF_Q + NS * Q_BYTES;
-    static constexpr uint32_t OFF_STAT = OFF_DO + NS * Q_BYTES;       // float lse[2][BQ], delta[2][BQ]
+    static constexpr uint32_t PS_BYTES = PS_SMEM ? BMK * BQ * 2 : 0;  // P^T / dS^T tile when staged in shared memory
+    static constexpr uint32_t OFF_PS = OFF_DO + NS * Q_BYTES, OFF_DSS = OFF_PS + PS_BYTES;
+    static constexpr uint32_t OFF_STAT = OFF_DSS + PS_BYTES;          // float lse[2][BQ], delta[2][BQ]
     static constexpr uint32_t OFF_BAR = OFF_STAT + 4 * BQ * 4;
     // barriers: kv_full, s_full, dp_full, s_free, pds_full, pds_done, q_full/q_empty[NS], do_full/do_empty[NS]
     static constexpr int N_BARS = 6 + 4 * NS;
@@ -388,10 +401,11 @@ struct BwdDkvCfg {
     // tensor memory: S^T [BQ] | dP^T [BQ] | dK [D] | dV [D] | P^T fp16 [BQ/2] | dS^T fp16 [BQ/2]
     static constexpr uint32_t COL_S = 0, COL_DP = BQ, COL_DK = 2 * BQ, COL_DV = 2 * BQ + D, COL_P = 2 * BQ + 2 * D,
                               COL_DS = 2 * BQ + 2 * D + BQ / 2;
-    static constexpr uint32_t COLS_USED = 3 * BQ + 2 * D;
+    static constexpr uint32_t COLS_USED = (PS_SMEM ? 2 : 3) * BQ + 2 * D;
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
-    static_assert(D % 64 == 0 && BQ % 32 == 0 && COLS_USED <= 512 && SMEM_BYTES <= 232448, "tile shape");
+    static_assert(D % 64 == 0 && CW % 32 == 0 && (D / 32) % WGS == 0 && 2 * BQ <= 128 * WGS && COLS_USED <= 512 &&
+                      SMEM_BYTES <= 232448 && (!PS_SMEM || BQ == 64), "tile shape");
 };
 
 template <class Cfg>
@@ -433,8 +447,8 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         ptx::mbar_init(kv_full, 1);
         ptx::mbar_init(s_full, 1);
         ptx::mbar_init(dp_full, 1);
-        ptx::mbar_init(s_free, 4);
-        ptx::mbar_init(pds_full, 4);
+        ptx::mbar_init(s_free, 4 * Cfg::WGS);
+        ptx::mbar_init(pds_full, 4 * Cfg::WGS);
         ptx::mbar_init(pds_done, 1);
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(q_full + 8 * s, 1);
@@ -512,6 +526,8 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const uint32_t do_lo = ptx::smem_desc_sw128_lo(do_s, 16);
             const uint32_t qmn_lo = ptx::smem_desc_sw128_lo(q_s, Cfg::Q_PANEL);
             const uint32_t domn_lo = ptx::smem_desc_sw128_lo(do_s, Cfg::Q_PANEL);
+            const uint32_t ps_lo = ptx::smem_desc_sw128_lo(sbase + Cfg::OFF_PS, 16);
+            const uint32_t dss_lo = ptx::smem_desc_sw128_lo(sbase + Cfg::OFF_DSS, 16);
             const uint32_t t_s = tmem + Cfg::COL_S, t_dp = tmem + Cfg::COL_DP, t_dk = tmem + Cfg::COL_DK,
                            t_dv = tmem + Cfg::COL_DV, t_p = tmem + Cfg::COL_P, t_ds = tmem + Cfg::COL_DS;
             bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
@@ -563,14 +579,24 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const uint32_t st_off = (uint32_t)s * (Cfg::Q_BYTES >> 4);
                 if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < BQ / 16; ++kk)
-                        ptx::mma_ts(t_dv, t_p + kk * 8, ptx::make_desc(domn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi),
-                                    idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BQ / 16; ++kk) {
+                        const uint64_t bdesc = ptx::make_desc(domn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi);
+                        const uint32_t acc = (t > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (Cfg::PS_SMEM)
+                            ptx::mma_ss(t_dv, ptx::make_desc(ps_lo + ((kk * 32) >> 4), desc_hi), bdesc, idesc_g, acc);
+                        else
+                            ptx::mma_ts(t_dv, t_p + kk * 8, bdesc, idesc_g, acc);
+                    }
                     ptx::mma_commit(do_empty + 8 * s);
 #pragma unroll
-                    for (int kk = 0; kk < BQ / 16; ++kk)
-                        ptx::mma_ts(t_dk, t_ds + kk * 8, ptx::make_desc(qmn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi),
-                                    idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BQ / 16; ++kk) {
+                        const uint64_t bdesc = ptx::make_desc(qmn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi);
+                        const uint32_t acc = (t > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (Cfg::PS_SMEM)
+                            ptx::mma_ss(t_dk, ptx::make_desc(dss_lo + ((kk * 32) >> 4), desc_hi), bdesc, idesc_g, acc);
+                        else
+                            ptx::mma_ts(t_dk, t_ds + kk * 8, bdesc, idesc_g, acc);
+                    }
                     ptx::mma_commit(q_empty + 8 * s);
                     ptx::mma_commit(pds_done);
                 }
@@ -579,14 +605,17 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, BWD_ERR_MMA); }
         }
     } else {
+        constexpr int CW = Cfg::CW;
         const int quarter = warp & 3;
+        const int wg = (warp - 2) >> 2;
+        const int c0 = wg * CW;                     // this warpgroup's first query column of every tile
         const int r = quarter * 32 + lane;          // key row inside the tile = TMEM lane
         const int key = key0 + r;
-        const int st = tid - 64;                    // 0..127 among the four row warps
+        const int st = tid - 64;                    // 0 .. 128*WGS-1 among the row warps
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const uint32_t t_s = tmem + lane_base + Cfg::COL_S, t_dp = tmem + lane_base + Cfg::COL_DP,
+        const uint32_t t_s = tmem + lane_base + Cfg::COL_S + c0, t_dp = tmem + lane_base + Cfg::COL_DP + c0,
                        t_dk = tmem + lane_base + Cfg::COL_DK, t_dv = tmem + lane_base + Cfg::COL_DV,
-                       t_p = tmem + lane_base + Cfg::COL_P, t_ds = tmem + lane_base + Cfg::COL_DS;
+                       t_p = tmem + lane_base + Cfg::COL_P + c0 / 2, t_ds = tmem + lane_base + Cfg::COL_DS + c0 / 2;
         const bool key_ok = key < kv_limit;
         bool ok = run;
         auto arrive_warp = [&](uint32_t bar) {
@@ -595,7 +624,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (lane == 0) ptx::mbar_arrive(bar);
         };
         for (int t = 0; t < n_it; ++t) {
-            // All four warps take every iteration's named barrier, also after a failed wait, so
+            // All row warps take every iteration's named barrier, also after a failed wait, so
             // that none of them is left behind at it.
             const int bhq = bh0 + t / per_head;
             const int qr0 = (i_start + t % per_head) * BQ;
@@ -607,34 +636,36 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const int qrow = qr0 + st - BQ;
                 st_delta[st - BQ] = qrow < p.Sq ? p.delta[(size_t)bhq * p.Sq + qrow] : 0.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if constexpr (Cfg::WGS == 1) asm volatile("bar.sync 1, 128;" ::: "memory");
+            else asm volatile("bar.sync 1, 256;" ::: "memory");
             if (!ok) continue;
             ok = ptx::mbar_wait(s_full, (uint32_t)t & 1u, abort_flag);
             if (!ok) continue;
             ptx::tc_fence_after_sync();
-            uint32_t sv[BQ], dpv[BQ];
-            ptx::tmem_ld_cols<BQ>(t_s, sv);
+            uint32_t sv[CW], dpv[CW];
+            ptx::tmem_ld_cols<CW>(t_s, sv);
             ok = ptx::mbar_wait(dp_full, (uint32_t)t & 1u, abort_flag);
             if (!ok) continue;
             ptx::tc_fence_after_sync();
-            ptx::tmem_ld_cols<BQ>(t_dp, dpv);
+            ptx::tmem_ld_cols<CW>(t_dp, dpv);
             ptx::tmem_wait_ld();
-            ptx::reg_fence_cols<BQ>(sv);
-            ptx::reg_fence_cols<BQ>(dpv);
+            ptx::reg_fence_cols<CW>(sv);
+            ptx::reg_fence_cols<CW>(dpv);
             arrive_warp(s_free);
-            const bool need_mask = p.causal && (key0 + BMK - 1 > qr0);
-            uint32_t pp[BQ / 2], pd[BQ / 2];
+            const int qc0 = qr0 + c0;               // first query of this warpgroup's columns
+            const bool need_mask = p.causal && (key0 + BMK - 1 > qc0);
+            uint32_t pp[CW / 2], pd[CW / 2];
 #pragma unroll
-            for (int i = 0; i < BQ; i += 2) {
-                float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -st_lse[i]));
-                float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -st_lse[i + 1]));
+            for (int i = 0; i < CW; i += 2) {
+                float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -st_lse[c0 + i]));
+                float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -st_lse[c0 + i + 1]));
                 if (!key_ok) { p0 = 0.f; p1 = 0.f; }
                 if (need_mask) {
-                    if (key > qr0 + i) p0 = 0.f;
-                    if (key > qr0 + i + 1) p1 = 0.f;
+                    if (key > qc0 + i) p0 = 0.f;
+                    if (key > qc0 + i + 1) p1 = 0.f;
                 }
-                const float d0 = p0 * (__uint_as_float(dpv[i]) - st_delta[i]) * p.scale;
-                const float d1 = p1 * (__uint_as_float(dpv[i + 1]) - st_delta[i + 1]) * p.scale;
+                const float d0 = p0 * (__uint_as_float(dpv[i]) - st_delta[c0 + i]) * p.scale;
+                const float d1 = p1 * (__uint_as_float(dpv[i + 1]) - st_delta[c0 + i + 1]) * p.scale;
                 pp[i / 2] = ptx::pack_half2(p0, p1);
                 pd[i / 2] = ptx::pack_half2(d0, d1);
             }
@@ -643,9 +674,21 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 if (!ok) continue;
                 ptx::tc_fence_after_sync();
             }
-            ptx::tmem_st_cols<BQ / 2>(t_p, pp);
-            ptx::tmem_st_cols<BQ / 2>(t_ds, pd);
-            ptx::tmem_wait_st();
+            if constexpr (Cfg::PS_SMEM) {
+                // row r of the [128 keys][64 queries] tile: 128 bytes = 8 chunks of 8 halves, chunk ^= r % 8
+                const uint32_t prow = sbase + Cfg::OFF_PS + (uint32_t)r * 128, drow = sbase + Cfg::OFF_DSS + (uint32_t)r * 128;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t sw = ((uint32_t)ch ^ (uint32_t)(r & 7)) << 4;
+                    ptx::st_shared_v4(prow + sw, pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
+                    ptx::st_shared_v4(drow + sw, pd[ch * 4], pd[ch * 4 + 1], pd[ch * 4 + 2], pd[ch * 4 + 3]);
+                }
+                ptx::fence_proxy_async_smem();
+            } else {
+                ptx::tmem_st_cols<CW / 2>(t_p, pp);
+                ptx::tmem_st_cols<CW / 2>(t_ds, pd);
+                ptx::tmem_wait_st();
+            }
             arrive_warp(pds_full);
         }
         const size_t gbase = ((size_t)kvh * p.Sk + key) * D;
@@ -654,7 +697,8 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (ok) {
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int cc = 0; cc < D / 32 / Cfg::WGS; ++cc) {
+                    const int c = cc * Cfg::WGS + wg;          // the warpgroups share the row's chunks
                     uint32_t o[32];
                     ptx::tmem_ld32(t_dk + c * 32, o);
                     ptx::tmem_wait_ld();
