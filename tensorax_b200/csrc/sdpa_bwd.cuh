@@ -311,18 +311,21 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             arrive_warp(s_free);
             const bool need_mask = (kv0 + CW > kv_limit) || (p.causal && (kv0 + CW - 1 > q0));
             uint32_t pk[CW / 2];
+            // packed fp32 pairs: x = s*c - lse, t = dP*scale - D*scale, dS = P*t
+            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse, -lse);
+            const float2 s2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
-                float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse));
-                float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -lse));
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), c2, nl2);
+                float2 pr = make_float2(ptx::ex2_approx(x.x), ptx::ex2_approx(x.y));
                 if (need_mask) {
                     const int k0 = kv0 + i, k1 = k0 + 1;
-                    if (!(k0 < kv_limit && (!p.causal || k0 <= row))) p0 = 0.f;
-                    if (!(k1 < kv_limit && (!p.causal || k1 <= row))) p1 = 0.f;
+                    if (!(k0 < kv_limit && (!p.causal || k0 <= row))) pr.x = 0.f;
+                    if (!(k1 < kv_limit && (!p.causal || k1 <= row))) pr.y = 0.f;
                 }
-                const float d0 = p0 * (__uint_as_float(dpv[i]) - delta) * p.scale;
-                const float d1 = p1 * (__uint_as_float(dpv[i + 1]) - delta) * p.scale;
-                pk[i / 2] = ptx::pack_half2(d0, d1);
+                const float2 tt = __ffma2_rn(make_float2(__uint_as_float(dpv[i]), __uint_as_float(dpv[i + 1])), s2, nd2);
+                const float2 ds = __fmul2_rn(pr, tt);
+                pk[i / 2] = ptx::pack_half2(ds.x, ds.y);
             }
             if (j > 0) {
                 ok = ptx::mbar_wait(dq_done, (uint32_t)(j - 1) & 1u, abort_flag);   // dS of tile j-1 consumed
@@ -419,7 +422,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V, q_s = sbase + Cfg::OFF_Q,
                    do_s = sbase + Cfg::OFF_DO;
-    float *stat = reinterpret_cast<float *>(smem + Cfg::OFF_STAT);   // [stage][0: lse, 1: delta][BQ]
+    float *stat = reinterpret_cast<float *>(smem + Cfg::OFF_STAT);   // [stage][0: -lse, 1: -delta*scale][BQ]
     const uint32_t bar0 = sbase + Cfg::OFF_BAR;
     const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, s_free = bar0 + 24,
                    pds_full = bar0 + 32, pds_done = bar0 + 40;
@@ -631,10 +634,10 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             float *st_lse = stat + (t & 1) * 2 * BQ, *st_delta = st_lse + BQ;
             if (st < BQ) {
                 const int qrow = qr0 + st;
-                st_lse[st] = qrow < p.Sq ? p.lse[(size_t)bhq * p.Sq + qrow] : INFINITY;   // +inf: P = 0
+                st_lse[st] = qrow < p.Sq ? -p.lse[(size_t)bhq * p.Sq + qrow] : -INFINITY;   // -lse; -inf: P = 0
             } else if (st < 2 * BQ) {
                 const int qrow = qr0 + st - BQ;
-                st_delta[st - BQ] = qrow < p.Sq ? p.delta[(size_t)bhq * p.Sq + qrow] : 0.f;
+                st_delta[st - BQ] = qrow < p.Sq ? -p.scale * p.delta[(size_t)bhq * p.Sq + qrow] : 0.f;   // -D*scale
             }
             if constexpr (Cfg::WGS == 1) asm volatile("bar.sync 1, 128;" ::: "memory");
             else asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -655,19 +658,24 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const int qc0 = qr0 + c0;               // first query of this warpgroup's columns
             const bool need_mask = p.causal && (key0 + BMK - 1 > qc0);
             uint32_t pp[CW / 2], pd[CW / 2];
+            const float2 c2 = make_float2(p.scale_log2, p.scale_log2), s2 = make_float2(p.scale, p.scale);
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
-                float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -st_lse[c0 + i]));
-                float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -st_lse[c0 + i + 1]));
-                if (!key_ok) { p0 = 0.f; p1 = 0.f; }
+                // packed fp32 pairs; the two queries' statistics sit side by side in shared memory
+                const float2 l2 = *reinterpret_cast<const float2 *>(st_lse + c0 + i);
+                const float2 dl = *reinterpret_cast<const float2 *>(st_delta + c0 + i);
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), c2, l2);
+                float2 pr = make_float2(ptx::ex2_approx(x.x), ptx::ex2_approx(x.y));
+                if (!key_ok) pr = make_float2(0.f, 0.f);
                 if (need_mask) {
-                    if (key > qc0 + i) p0 = 0.f;
-                    if (key > qc0 + i + 1) p1 = 0.f;
+                    if (key > qc0 + i) pr.x = 0.f;
+                    if (key > qc0 + i + 1) pr.y = 0.f;
                 }
-                const float d0 = p0 * (__uint_as_float(dpv[i]) - st_delta[c0 + i]) * p.scale;
-                const float d1 = p1 * (__uint_as_float(dpv[i + 1]) - st_delta[c0 + i + 1]) * p.scale;
-                pp[i / 2] = ptx::pack_half2(p0, p1);
-                pd[i / 2] = ptx::pack_half2(d0, d1);
+                const float2 tt = __ffma2_rn(make_float2(__uint_as_float(dpv[i]), __uint_as_float(dpv[i + 1])), s2,
+                                             dl);
+                const float2 ds = __fmul2_rn(pr, tt);
+                pp[i / 2] = ptx::pack_half2(pr.x, pr.y);
+                pd[i / 2] = ptx::pack_half2(ds.x, ds.y);
             }
             if (t > 0) {
                 ok = ptx::mbar_wait(pds_done, (uint32_t)(t - 1) & 1u, abort_flag);
