@@ -795,9 +795,9 @@ int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)
         // per SM and two row warpgroups, config-2 size).
         // d = 128: one CTA per SM for both, two row warpgroups, 128-key / 64-query tiles (all of tensor memory).
         if (d->d == 64)
-            rc = launch_bwd<64, txb::BwdDqCfg<64, 64, 2, 1>, txb::BwdDkvCfg<64, 64, 2, 1, true>>(d, st, status, dout_h, delta);
+            rc = launch_bwd<64, txb::BwdDqCfg<64, 64, 3, 1, 2>, txb::BwdDkvCfg<64, 64, 3, 1, true, 2>>(d, st, status, dout_h, delta);
         else
-            rc = launch_bwd<128, txb::BwdDqCfg<128, 128, 2, 2>, txb::BwdDkvCfg<128, 64, 2, 2>>(d, st, status, dout_h, delta);
+            rc = launch_bwd<128, txb::BwdDqCfg<128, 128, 3, 2, 2>, txb::BwdDkvCfg<128, 64, 3, 2, false, 3>>(d, st, status, dout_h, delta);
     }
     (void)cudaFreeAsync(ws, st);        // ordered after the kernels on `st`
     return rc;

@@ -74,9 +74,11 @@ __global__ void sdpa_bwd_prep_kernel(const float *__restrict__ dout, const OT *_
 
 // ------------------------------------------------------------------ dQ
 // WGS: row warpgroups (4 warps, one thread per TMEM lane each); with 2, each takes half of a tile's columns.
-template <int D_, int BN_, int NS_, int WGS_ = 1>
+// NS / NSV: depth of the K / V ring.  A K stage is read twice (S = Q K^T, later dQ += dS K) and only
+// then freed, so its ring is one deeper than V's, whose stage goes back right after dP = dO V^T.
+template <int D_, int BN_, int NS_, int WGS_ = 1, int NSV_ = 2>
 struct BwdDqCfg {
-    static constexpr int D = D_, BN = BN_, NS = NS_, BM = 128, WGS = WGS_;
+    static constexpr int D = D_, BN = BN_, NS = NS_, NSV = NSV_, BM = 128, WGS = WGS_;
     static constexpr int CW = BN / WGS;                      // tile columns per warpgroup
     static constexpr int THREADS = 64 + 128 * WGS;
     static constexpr int KP = D / 64;
@@ -84,9 +86,9 @@ struct BwdDqCfg {
     static constexpr uint32_t KV_BYTES = BN * D * 2;         // one K or V stage
     static constexpr uint32_t KV_PANEL = BN * 128;
     static constexpr uint32_t OFF_Q = 0, OFF_DO = Q_BYTES, OFF_K = 2 * Q_BYTES, OFF_V = OFF_K + NS * KV_BYTES;
-    static constexpr uint32_t OFF_BAR = OFF_V + NS * KV_BYTES;
-    // barriers: qdo_full, s_full, dp_full, s_free, ds_full, dq_done, k_full/k_empty[NS], v_full/v_empty[NS]
-    static constexpr int N_BARS = 6 + 4 * NS;
+    static constexpr uint32_t OFF_BAR = OFF_V + NSV * KV_BYTES;
+    // barriers: qdo_full, s_full, dp_full, s_free, ds_full, dq_done, k_full/k_empty[NS], v_full/v_empty[NSV]
+    static constexpr int N_BARS = 6 + 2 * NS + 2 * NSV;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
@@ -105,7 +107,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const BwdParams p)
 {
-    constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
+    constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, NSV = Cfg::NSV, BM = Cfg::BM;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t q_s = sbase + Cfg::OFF_Q, do_s = sbase + Cfg::OFF_DO, k_s = sbase + Cfg::OFF_K,
@@ -114,7 +116,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t qdo_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, s_free = bar0 + 24,
                    ds_full = bar0 + 32, dq_done = bar0 + 40;
     const uint32_t k_full = bar0 + 48, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS,
-                   v_empty = v_full + 8 * NS;
+                   v_empty = v_full + 8 * NSV;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
@@ -141,6 +143,8 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(k_full + 8 * s, 1);
             ptx::mbar_init(k_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < NSV; ++s) {
             ptx::mbar_init(v_full + 8 * s, 1);
             ptx::mbar_init(v_empty + 8 * s, 1);
         }
@@ -188,13 +192,15 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                                          pn * 64, j * BN, kvh);
                 }
                 __syncwarp();
-                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                const int sv_ = j % NSV;
+                const uint32_t phv = (uint32_t)(j / NSV) & 1u;
+                ok = ptx::mbar_wait(v_empty + 8 * sv_, phv ^ 1u, abort_flag);
                 if (!ok) break;
                 if (leader) {
-                    ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::KV_BYTES);
+                    ptx::mbar_arrive_expect_tx(v_full + 8 * sv_, Cfg::KV_BYTES);
 #pragma unroll
                     for (int pn = 0; pn < Cfg::KP; ++pn)
-                        ptx::tma_load_3d(v_s + s * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_v, v_full + 8 * s,
+                        ptx::tma_load_3d(v_s + sv_ * Cfg::KV_BYTES + pn * Cfg::KV_PANEL, &tm_v, v_full + 8 * sv_,
                                          pn * 64, j * BN, kvh);
                 }
                 __syncwarp();
@@ -232,17 +238,20 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     ptx::mma_commit(s_full);
                 }
                 __syncwarp();
-                if (!ptx::mbar_wait(v_full + 8 * s, ph, abort_flag)) return false;
+                const int sv_ = j % NSV;
+                const uint32_t phv = (uint32_t)(j / NSV) & 1u;
+                const uint32_t sv_off = (uint32_t)sv_ * (Cfg::KV_BYTES >> 4);
+                if (!ptx::mbar_wait(v_full + 8 * sv_, phv, abort_flag)) return false;
                 ptx::tc_fence_after_sync();
                 if (leader) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t a = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
                         const uint32_t bb = ((kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32) >> 4;
-                        ptx::mma_ss(t_dp, ptx::make_desc(do_lo + a, desc_hi), ptx::make_desc(v_lo + st_off + bb, desc_hi),
+                        ptx::mma_ss(t_dp, ptx::make_desc(do_lo + a, desc_hi), ptx::make_desc(v_lo + sv_off + bb, desc_hi),
                                     idesc_s, kk > 0);
                     }
-                    ptx::mma_commit(v_empty + 8 * s);
+                    ptx::mma_commit(v_empty + 8 * sv_);
                     ptx::mma_commit(dp_full);
                 }
                 __syncwarp();
@@ -381,9 +390,11 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // ------------------------------------------------------------------ dK, dV
 // PS_SMEM: P^T and dS^T are staged in shared memory (SS-form MMAs) instead of tensor memory, which
 // brings the CTA down to 256 tensor-memory columns at d = 64 so that two CTAs share an SM.
-template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false>
+// NS / NSD: depth of the Q / dO ring; both stages are read twice (K-major for S^T / dP^T, MN-major for
+// dK / dV) and stay occupied until the second read is done.
+template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false, int NSD_ = NS_>
 struct BwdDkvCfg {
-    static constexpr int D = D_, BQ = BQ_, NS = NS_, BMK = 128, WGS = WGS_;
+    static constexpr int D = D_, BQ = BQ_, NS = NS_, NSD = NSD_, BMK = 128, WGS = WGS_;
     static constexpr bool PS_SMEM = PS_SMEM_;
     static constexpr int CW = BQ / WGS;                      // tile columns (queries) per warpgroup
     static constexpr int THREADS = 64 + 128 * WGS;
@@ -393,11 +404,11 @@ struct BwdDkvCfg {
     static constexpr uint32_t Q_PANEL = BQ * 128;
     static constexpr uint32_t OFF_K = 0, OFF_V = KV_BYTES, OFF_Q = 2 * KV_BYTES, OFF_DO = OFF_Q + NS * Q_BYTES;
     static constexpr uint32_t PS_BYTES = PS_SMEM ? BMK * BQ * 2 : 0;  // P^T / dS^T tile when staged in shared memory
-    static constexpr uint32_t OFF_PS = OFF_DO + NS * Q_BYTES, OFF_DSS = OFF_PS + PS_BYTES;
+    static constexpr uint32_t OFF_PS = OFF_DO + NSD * Q_BYTES, OFF_DSS = OFF_PS + PS_BYTES;
     static constexpr uint32_t OFF_STAT = OFF_DSS + PS_BYTES;          // float lse[2][BQ], delta[2][BQ]
     static constexpr uint32_t OFF_BAR = OFF_STAT + 4 * BQ * 4;
-    // barriers: kv_full, s_full, dp_full, s_free, pds_full, pds_done, q_full/q_empty[NS], do_full/do_empty[NS]
-    static constexpr int N_BARS = 6 + 4 * NS;
+    // barriers: kv_full, s_full, dp_full, s_free, pds_full, pds_done, q_full/q_empty[NS], do_full/do_empty[NSD]
+    static constexpr int N_BARS = 6 + 2 * NS + 2 * NSD;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
@@ -417,7 +428,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const BwdParams p)
 {
-    constexpr int D = Cfg::D, BQ = Cfg::BQ, NS = Cfg::NS, BMK = Cfg::BMK;
+    constexpr int D = Cfg::D, BQ = Cfg::BQ, NS = Cfg::NS, NSD = Cfg::NSD, BMK = Cfg::BMK;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V, q_s = sbase + Cfg::OFF_Q,
@@ -427,7 +438,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, s_free = bar0 + 24,
                    pds_full = bar0 + 32, pds_done = bar0 + 40;
     const uint32_t q_full = bar0 + 48, q_empty = q_full + 8 * NS, do_full = q_empty + 8 * NS,
-                   do_empty = do_full + 8 * NS;
+                   do_empty = do_full + 8 * NSD;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
@@ -456,6 +467,8 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int s = 0; s < NS; ++s) {
             ptx::mbar_init(q_full + 8 * s, 1);
             ptx::mbar_init(q_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < NSD; ++s) {
             ptx::mbar_init(do_full + 8 * s, 1);
             ptx::mbar_init(do_empty + 8 * s, 1);
         }
@@ -504,13 +517,15 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                         ptx::tma_load_3d(q_s + s * Cfg::Q_BYTES + pn * Cfg::Q_PANEL, &tm_q, q_full + 8 * s, pn * 64, qr0, bhq);
                 }
                 __syncwarp();
-                ok = ptx::mbar_wait(do_empty + 8 * s, ph ^ 1u, abort_flag);
+                const int sd = t % NSD;
+                const uint32_t phd = (uint32_t)(t / NSD) & 1u;
+                ok = ptx::mbar_wait(do_empty + 8 * sd, phd ^ 1u, abort_flag);
                 if (!ok) break;
                 if (leader) {
-                    ptx::mbar_arrive_expect_tx(do_full + 8 * s, Cfg::Q_BYTES);
+                    ptx::mbar_arrive_expect_tx(do_full + 8 * sd, Cfg::Q_BYTES);
 #pragma unroll
                     for (int pn = 0; pn < Cfg::KP; ++pn)
-                        ptx::tma_load_3d(do_s + s * Cfg::Q_BYTES + pn * Cfg::Q_PANEL, &tm_do, do_full + 8 * s, pn * 64, qr0,
+                        ptx::tma_load_3d(do_s + sd * Cfg::Q_BYTES + pn * Cfg::Q_PANEL, &tm_do, do_full + 8 * sd, pn * 64, qr0,
                                          bhq);
                 }
                 __syncwarp();
@@ -551,14 +566,17 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     ptx::mma_commit(s_full);
                 }
                 __syncwarp();
-                if (!ptx::mbar_wait(do_full + 8 * s, ph, abort_flag)) return false;
+                const int sd = t % NSD;
+                const uint32_t phd = (uint32_t)(t / NSD) & 1u;
+                const uint32_t sd_off = (uint32_t)sd * (Cfg::Q_BYTES >> 4);
+                if (!ptx::mbar_wait(do_full + 8 * sd, phd, abort_flag)) return false;
                 ptx::tc_fence_after_sync();
                 if (leader) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t a = ((kk >> 2) * (BMK * 128) + (kk & 3) * 32) >> 4;
                         const uint32_t bb = ((kk >> 2) * Cfg::Q_PANEL + (kk & 3) * 32) >> 4;
-                        ptx::mma_ss(t_dp, ptx::make_desc(v_lo + a, desc_hi), ptx::make_desc(do_lo + st_off + bb, desc_hi),
+                        ptx::mma_ss(t_dp, ptx::make_desc(v_lo + a, desc_hi), ptx::make_desc(do_lo + sd_off + bb, desc_hi),
                                     idesc_s, kk > 0);
                     }
                     ptx::mma_commit(dp_full);
@@ -578,19 +596,19 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 ok = ptx::mbar_wait(pds_full, (uint32_t)t & 1u, abort_flag);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                const int s = t % NS;
-                const uint32_t st_off = (uint32_t)s * (Cfg::Q_BYTES >> 4);
+                const int s = t % NS, sd = t % NSD;
+                const uint32_t st_off = (uint32_t)s * (Cfg::Q_BYTES >> 4), sd_off = (uint32_t)sd * (Cfg::Q_BYTES >> 4);
                 if (leader) {
 #pragma unroll
                     for (int kk = 0; kk < BQ / 16; ++kk) {
-                        const uint64_t bdesc = ptx::make_desc(domn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi);
+                        const uint64_t bdesc = ptx::make_desc(domn_lo + sd_off + kk * ((16 * 128) >> 4), desc_hi);
                         const uint32_t acc = (t > 0 || kk > 0) ? 1u : 0u;
                         if constexpr (Cfg::PS_SMEM)
                             ptx::mma_ss(t_dv, ptx::make_desc(ps_lo + ((kk * 32) >> 4), desc_hi), bdesc, idesc_g, acc);
                         else
                             ptx::mma_ts(t_dv, t_p + kk * 8, bdesc, idesc_g, acc);
                     }
-                    ptx::mma_commit(do_empty + 8 * s);
+                    ptx::mma_commit(do_empty + 8 * sd);
 #pragma unroll
                     for (int kk = 0; kk < BQ / 16; ++kk) {
                         const uint64_t bdesc = ptx::make_desc(qmn_lo + st_off + kk * ((16 * 128) >> 4), desc_hi);
