@@ -172,3 +172,10 @@ def test_tensor_round_trip_and_repeat_interleave_on_host():
     assert np.array_equal(r[0, 0], r[0, 1]) and np.array_equal(r[0, 2], x.numpy()[0, 1])
     with pytest.raises(ValueError):
         ts.Tensor([1.0], device="tpu")
+
+
+@pytest.mark.skipif(_lib.cuda_is_available(), reason="checks the no-device behaviour")
+def test_workloads_cli_refuses_to_run_without_a_device():
+    from tensorax_b200 import workloads
+    with pytest.raises(RuntimeError, match="no CPU compute path"):
+        workloads.main(["bwd", "--batch", "1", "--heads", "1", "--seq", "128", "--d", "64", "--iters", "1"])
