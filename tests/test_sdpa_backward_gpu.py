@@ -199,3 +199,59 @@ def test_autograd_through_the_python_api():
     assert o2.requires_grad
     with pytest.raises(RuntimeError, match="kept no row statistics"):
         o2.backward(ts.Tensor(np.ones((1, 4, 16, 16), np.float32), device="cuda"))
+
+
+def test_sharded_backward_equals_the_single_device_run_bitwise():
+    """The forward's partition (whole (batch, K/V-head) units per rank, no collective) carries over to the
+    backward: a unit's dK/dV sum only over its own query heads.  Each rank's slab through the same kernels,
+    reassembled: identical bits."""
+    from tensorax_b200 import sharding
+    B, Hq, Hkv, S, d = 2, 8, 2, 384, 64
+    q = seeded(97, B, Hq, S, d).astype(np.float16)
+    k, v = (seeded(98 + j, B, Hkv, S, d).astype(np.float16) for j in range(2))
+    g = seeded(100, B, Hq, S, d).astype(np.float32)
+    lens = [384, 200]
+    _, _, fq, fk, fv = backward_device(q, k, v, g, causal=True, kv_lens=lens)
+    for world in (2, 4):
+        dq, dk, dv = np.zeros_like(fq), np.zeros_like(fk), np.zeros_like(fv)
+        for r in range(world):
+            sh = sharding.partition(B, Hkv, Hq, world, r)
+            qs, ks, vs, ls = sharding.shard_arrays(sh, q, k, v, lens)
+            gs = g.reshape(B * Hkv, sh.group, S, d)[sh.unit_begin:sh.unit_end]
+            _, _, lq, lk, lv = backward_device(qs, ks, vs, gs, causal=True, kv_lens=ls)
+            sharding.place_output(sh, dq, lq)
+            dk.reshape(B * Hkv, S, d)[sh.unit_begin:sh.unit_end] = lk.reshape(-1, S, d)
+            dv.reshape(B * Hkv, S, d)[sh.unit_begin:sh.unit_end] = lv.reshape(-1, S, d)
+        for a, b in ((dq, fq), (dk, fk), (dv, fv)):
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_forward_and_backward(seed):
+    """Seeded random ragged shapes, masks and head groupings: forward (all tensor-core head dims, fp32 or fp16
+    result) and, where the backward kernels exist, all three gradients."""
+    rng = np.random.default_rng(1000 + seed)
+    d = int(rng.choice([64, 128, 256, 512]))
+    Hkv = int(rng.integers(1, 4))
+    Hq = Hkv * int(rng.integers(1, 4))
+    B = int(rng.integers(1, 4))
+    Sq = int(rng.integers(1, 700 if d <= 128 else 300))
+    Sk = int(rng.integers(1, 700 if d <= 128 else 300))
+    causal = bool(rng.integers(0, 2))
+    lens = [int(x) for x in rng.integers(1, Sk + 1, size=B)] if rng.integers(0, 2) else None
+    out_f16 = bool(rng.integers(0, 2))
+    q = seeded(2000 + seed, B, Hq, Sq, d).astype(np.float16)
+    k = seeded(3000 + seed, B, Hkv, Sk, d).astype(np.float16)
+    v = seeded(4000 + seed, B, Hkv, Sk, d).astype(np.float16)
+    ref = oracle.sdpa_structured(widen(q), widen(k), widen(v), causal=causal, kv_lens=lens)
+    if d > 128:
+        got, tc = sdpa_device(q, k, v, causal=causal, kv_lens=lens, flags=_lib.TX_SDPA_OUT_F16 if out_f16 else 0)
+        assert tc
+        assert_close_fp16(got.astype(np.float32), ref)
+        return
+    g = seeded(5000 + seed, B, Hq, Sq, d).astype(np.float32)
+    out, lse, dq, dk, dv = backward_device(q, k, v, g, causal=causal, kv_lens=lens, out_f16=out_f16)
+    assert_close_fp16(out.astype(np.float32), ref)
+    rq, rk, rv, _ = oracle.sdpa_backward(widen(q), widen(k), widen(v), g, causal=causal, kv_lens=lens)
+    for got, r, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
+        assert_grad_close(got, r, f"{name} {(B, Hq, Hkv, Sq, Sk, d, causal, lens, out_f16)}")
