@@ -177,7 +177,7 @@ TX_API int tx_profile_sections_sdpa(const tx_sdpa_desc *desc, long long *ticks32
  *      dQ = dS K, dK = dS^T Q), which the reference evaluates with dense [Sq,Sk] temporaries through
  *      Tensor.transpose/matmul.  Here: flash-style on the tensor cores, P rebuilt from the forward's `lse`,
  *      gradients of grouped K/V heads summed over their query heads, no atomics (bitwise reproducible).
- *      fp16 q/k/v with d in {64,128}, implicit masks only (causal / kv_lens); asynchronous on `stream`
+ *      fp16 q/k/v with d in {64,128,256}, implicit masks only (causal / kv_lens); asynchronous on `stream`
  *      (tx_sdpa_finish reports kernel-side failures).  Takes 2*batch*q_heads*seq_q*(d+2) bytes from the
  *      device's stream-ordered pool for the fp16 copy of `dout` and the row sums, and returns them. */
 typedef struct tx_sdpa_bwd_desc {

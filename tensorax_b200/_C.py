@@ -219,8 +219,13 @@ def _validate(query, key, value, mask, who="SDPA"):
     return B, H, Hkv, Sq, Sk, dk, dv
 
 
+def synchronize() -> None:
+    """Wait for everything enqueued with ``sync=False`` and raise if a kernel reported a failure."""
+    _lib.check(_lib.load().tx_sdpa_finish(None))
+
+
 def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="SDPA", out_dtype="float32",
-             want_lse=False):
+             want_lse=False, sync=True):
     B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, mask, who)
     if query.device != "cuda":
         raise RuntimeError(
@@ -254,15 +259,18 @@ def _forward(query, key, value, mask, causal=False, kv_lens=None, flags=0, who="
         flags=int(flags), stream=None, lse=lse.data_ptr if lse is not None else None)
     lib = _lib.load()
     _lib.check(lib.tx_sdpa_forward(ctypes.byref(desc)))
-    _lib.check(lib.tx_sdpa_finish(None))   # the reference launchers return a finished result
+    if sync:
+        _lib.check(lib.tx_sdpa_finish(None))   # the reference launchers return a finished result
+    # sync=False: the launch is stream-ordered; buffers freed meanwhile (the key lengths above) go back to
+    # the pool in stream order, so nothing is reused before the kernel has read it
     return (out, lse) if want_lse else out
 
 
 def sdpa_backward_supported(query, key, value, mask) -> bool:
-    """Shapes the backward kernels take: float16 CUDA tensors, d_k == d_v in {64, 128}, no dense mask."""
+    """Shapes the backward kernels take: float16 CUDA tensors, d_k == d_v in {64, 128, 256}, no dense mask."""
     return (mask is None and query.device == "cuda" and query.dtype in ("float16", "half")
             and key.dtype == query.dtype and value.dtype == query.dtype
-            and query._shape[3] == value._shape[3] and query._shape[3] in (64, 128))
+            and query._shape[3] == value._shape[3] and query._shape[3] in (64, 128, 256))
 
 
 def scaled_dot_product_attention_backward(query, key, value, out, lse, grad, causal=False, kv_lens=None):
@@ -273,7 +281,7 @@ def scaled_dot_product_attention_backward(query, key, value, out, lse, grad, cau
     the forward returned with ``want_lse``."""
     B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, None, "SDPA backward")
     if not sdpa_backward_supported(query, key, value, None):
-        raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128} and "
+        raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128, 256} and "
                            "implicit (causal / kv_lens) masks")
     if list(grad._shape) != [B, H, Sq, dv] or grad.dtype != "float32" or grad.device != "cuda":
         raise RuntimeError("SDPA backward: grad must be a float32 CUDA tensor shaped like the output")
@@ -353,10 +361,12 @@ def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
 
 
 def scaled_dot_product_attention_ex(query, key, value, mask=None, causal=False, kv_lens=None,
-                                    flags=0, out_dtype="float32", want_lse=False):
+                                    flags=0, out_dtype="float32", want_lse=False, sync=True):
     """No reference counterpart: implicit masks for sizes where the dense
     [B,H,Sq,Sk] mask cannot exist.  ``causal``: key j visible to query i iff
     j <= i; ``kv_lens``: per-batch count of valid keys; ``out_dtype``: 'float32'
-    (what every reference entry returns) or 'float16' (half the result bytes)."""
+    (what every reference entry returns) or 'float16' (half the result bytes); ``sync=False``: return
+    right after the launch (the reference's launchers end in cudaDeviceSynchronize, csrc/cuda/kernels/attn.cu:1519-1520);
+    call ``synchronize()`` before reading the result on the host -- device-side consumers need nothing."""
     return _forward(query, key, value, mask, causal=causal, kv_lens=kv_lens, flags=flags, out_dtype=out_dtype,
-                    want_lse=want_lse)
+                    want_lse=want_lse, sync=sync)

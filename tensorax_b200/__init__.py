@@ -11,6 +11,7 @@ There is no CPU path and no fallback: without the built library, or without a
 CUDA device, compute calls raise.
 """
 from . import functional, nn  # noqa: F401
+from ._C import synchronize
 from ._lib import cuda_is_available
 from .tensor import Tensor
 
@@ -18,4 +19,4 @@ __version__ = "0.1.0"
 cpu = "cpu"
 cuda = "cuda"
 
-__all__ = ["Tensor", "functional", "nn", "cuda_is_available", "cpu", "cuda"]
+__all__ = ["Tensor", "functional", "nn", "cuda_is_available", "synchronize", "cpu", "cuda"]

@@ -283,7 +283,8 @@ int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __
         if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, D, DkvCfg::BMK)) return rc;
         TX_CUDA(cudaFuncSetAttribute(txb::sdpa_bwd_dkv_kernel<DkvCfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)DkvCfg::SMEM_BYTES));
-        dim3 grid((unsigned)((d->seq_k + DkvCfg::BMK - 1) / DkvCfg::BMK), (unsigned)(d->batch * d->kv_heads));
+        dim3 grid((unsigned)((d->seq_k + DkvCfg::BMK - 1) / DkvCfg::BMK), (unsigned)(d->batch * d->kv_heads),
+                  (unsigned)DkvCfg::ZS);
         txb::sdpa_bwd_dkv_kernel<DkvCfg><<<grid, DkvCfg::THREADS, DkvCfg::SMEM_BYTES, st>>>(tq, tdo, tk, tv, p);
         g_launches++;
         TX_CUDA(cudaGetLastError());
@@ -762,8 +763,8 @@ int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)
     if (d->q_heads % d->kv_heads != 0)
         return fail(TX_ERR_INVALID, "SDPA backward: q_heads %lld not a multiple of kv_heads %lld",
                     (long long)d->q_heads, (long long)d->kv_heads);
-    if (d->d != 64 && d->d != 128)
-        return fail(TX_ERR_UNSUPPORTED, "SDPA backward: built for d in {64, 128}, got %lld", (long long)d->d);
+    if (d->d != 64 && d->d != 128 && d->d != 256)
+        return fail(TX_ERR_UNSUPPORTED, "SDPA backward: built for d in {64, 128, 256}, got %lld", (long long)d->d);
     if (d->batch * d->q_heads > 65535 || d->seq_q > 0x3fffffffLL || d->seq_k > 0x3fffffffLL)
         return fail(TX_ERR_UNSUPPORTED, "SDPA backward: dimension too large");
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
@@ -796,8 +797,14 @@ int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)
         // d = 128: one CTA per SM for both, two row warpgroups, 128-key / 64-query tiles (all of tensor memory).
         if (d->d == 64)
             rc = launch_bwd<64, txb::BwdDqCfg<64, 64, 3, 1, 2>, txb::BwdDkvCfg<64, 64, 3, 1, true, 2>>(d, st, status, dout_h, delta);
-        else
+        else if (d->d == 128)
             rc = launch_bwd<128, txb::BwdDqCfg<128, 128, 3, 2, 2>, txb::BwdDkvCfg<128, 64, 3, 2, false, 3>>(d, st, status, dout_h, delta);
+        else
+            // d = 256: dQ alone takes 256 tensor-memory columns (64-key tiles, single V stage: 224 KB of shared
+            // memory); two CTAs per key tile each own 128 columns of dK and dV, with 32-query tiles so that two
+            // stages each of Q and dO fit beside the resident K and V (a stage stays occupied from its first
+            // read to its second, so one stage per ring would deadlock the MMA warp).
+            rc = launch_bwd<256, txb::BwdDqCfg<256, 64, 2, 1, 1>, txb::BwdDkvCfg<256, 32, 2, 1, false, 2, 2>>(d, st, status, dout_h, delta);
     }
     (void)cudaFreeAsync(ws, st);        // ordered after the kernels on `st`
     return rc;

@@ -392,9 +392,12 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // brings the CTA down to 256 tensor-memory columns at d = 64 so that two CTAs share an SM.
 // NS / NSD: depth of the Q / dO ring; both stages are read twice (K-major for S^T / dP^T, MN-major for
 // dK / dV) and stay occupied until the second read is done.
-template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false, int NSD_ = NS_>
+// ZS: CTAs (grid.z) that share one key tile, each accumulating D/ZS columns of dK and dV (both form the whole
+// S^T and dP^T): at d = 256 the two accumulators of one CTA would need all 512 tensor-memory columns.
+template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false, int NSD_ = NS_, int ZS_ = 1>
 struct BwdDkvCfg {
-    static constexpr int D = D_, BQ = BQ_, NS = NS_, NSD = NSD_, BMK = 128, WGS = WGS_;
+    static constexpr int D = D_, BQ = BQ_, NS = NS_, NSD = NSD_, BMK = 128, WGS = WGS_, ZS = ZS_;
+    static constexpr int DA = D / ZS;                        // gradient columns this CTA accumulates
     static constexpr bool PS_SMEM = PS_SMEM_;
     static constexpr int CW = BQ / WGS;                      // tile columns (queries) per warpgroup
     static constexpr int THREADS = 64 + 128 * WGS;
@@ -413,13 +416,14 @@ struct BwdDkvCfg {
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
     // tensor memory: S^T [BQ] | dP^T [BQ] | dK [D] | dV [D] | P^T fp16 [BQ/2] | dS^T fp16 [BQ/2]
-    static constexpr uint32_t COL_S = 0, COL_DP = BQ, COL_DK = 2 * BQ, COL_DV = 2 * BQ + D, COL_P = 2 * BQ + 2 * D,
-                              COL_DS = 2 * BQ + 2 * D + BQ / 2;
-    static constexpr uint32_t COLS_USED = (PS_SMEM ? 2 : 3) * BQ + 2 * D;
+    static constexpr uint32_t COL_S = 0, COL_DP = BQ, COL_DK = 2 * BQ, COL_DV = 2 * BQ + DA, COL_P = 2 * BQ + 2 * DA,
+                              COL_DS = 2 * BQ + 2 * DA + BQ / 2;
+    static constexpr uint32_t COLS_USED = (PS_SMEM ? 2 : 3) * BQ + 2 * DA;
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
-    static_assert(D % 64 == 0 && CW % 32 == 0 && (D / 32) % WGS == 0 && 2 * BQ <= 128 * WGS && COLS_USED <= 512 &&
-                      SMEM_BYTES <= 232448 && (!PS_SMEM || BQ == 64), "tile shape");
+    static_assert(D % 64 == 0 && DA % 64 == 0 && CW % 32 == 0 && (DA / 32) % WGS == 0 && 2 * BQ <= 128 * WGS &&
+                      COLS_USED <= 512 && SMEM_BYTES <= 232448 && (!PS_SMEM || BQ == 64), "tile shape");
+    static_assert(NS >= 2 && NSD >= 2, "Q and dO stages are held from their first read to their second");
 };
 
 template <class Cfg>
@@ -428,7 +432,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const BwdParams p)
 {
-    constexpr int D = Cfg::D, BQ = Cfg::BQ, NS = Cfg::NS, NSD = Cfg::NSD, BMK = Cfg::BMK;
+    constexpr int D = Cfg::D, DA = Cfg::DA, BQ = Cfg::BQ, NS = Cfg::NS, NSD = Cfg::NSD, BMK = Cfg::BMK;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = ptx::smem_u32(smem);
     const uint32_t k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V, q_s = sbase + Cfg::OFF_Q,
@@ -444,6 +448,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int key0 = (int)blockIdx.x * BMK;
+    const int col0 = (int)blockIdx.z * DA;                      // first dK / dV column of this CTA
     const int kvh = blockIdx.y;                                 // b * Hkv + kv head
     const int b = kvh / p.Hkv;
     const int group = p.Hq / p.Hkv;
@@ -536,14 +541,16 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (run) {
             const bool leader = ptx::elect_one();
             constexpr uint32_t idesc_s = ptx::idesc_f16(BMK, BQ, false);    // S^T, dP^T: both operands K-major
-            constexpr uint32_t idesc_g = ptx::idesc_f16(BMK, D, true);      // dV, dK: B = dO / Q tile read MN-major
+            constexpr uint32_t idesc_g = ptx::idesc_f16(BMK, DA, true);     // dV, dK: B = dO / Q tile read MN-major
             constexpr uint32_t desc_hi = ptx::smem_desc_sw128_hi(1024);
             const uint32_t k_lo = ptx::smem_desc_sw128_lo(k_s, 16);
             const uint32_t v_lo = ptx::smem_desc_sw128_lo(v_s, 16);
             const uint32_t q_lo = ptx::smem_desc_sw128_lo(q_s, 16);
             const uint32_t do_lo = ptx::smem_desc_sw128_lo(do_s, 16);
-            const uint32_t qmn_lo = ptx::smem_desc_sw128_lo(q_s, Cfg::Q_PANEL);
-            const uint32_t domn_lo = ptx::smem_desc_sw128_lo(do_s, Cfg::Q_PANEL);
+            // MN-major reads start at this CTA's first 64-column panel
+            const uint32_t pan0 = (uint32_t)(col0 / 64) * Cfg::Q_PANEL;
+            const uint32_t qmn_lo = ptx::smem_desc_sw128_lo(q_s + pan0, Cfg::Q_PANEL);
+            const uint32_t domn_lo = ptx::smem_desc_sw128_lo(do_s + pan0, Cfg::Q_PANEL);
             const uint32_t ps_lo = ptx::smem_desc_sw128_lo(sbase + Cfg::OFF_PS, 16);
             const uint32_t dss_lo = ptx::smem_desc_sw128_lo(sbase + Cfg::OFF_DSS, 16);
             const uint32_t t_s = tmem + Cfg::COL_S, t_dp = tmem + Cfg::COL_DP, t_dk = tmem + Cfg::COL_DK,
@@ -717,13 +724,13 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
             arrive_warp(pds_full);
         }
-        const size_t gbase = ((size_t)kvh * p.Sk + key) * D;
+        const size_t gbase = ((size_t)kvh * p.Sk + key) * D + col0;
         if (run && ok) {
             ok = ptx::mbar_wait(pds_done, (uint32_t)(n_it - 1) & 1u, abort_flag);
             if (ok) {
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int cc = 0; cc < D / 32 / Cfg::WGS; ++cc) {
+                for (int cc = 0; cc < DA / 32 / Cfg::WGS; ++cc) {
                     const int c = cc * Cfg::WGS + wg;          // the warpgroups share the row's chunks
                     uint32_t o[32];
                     ptx::tmem_ld32(t_dk + c * 32, o);
@@ -752,7 +759,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, BWD_ERR_ROWS); }
         if (!run && *abort_flag == 0 && key < p.Sk) {
             // no query sees these keys: zero gradients
-            for (int i = 0; i < D; i += 4) {
+            for (int i = 0; i < DA; i += 4) {
                 *reinterpret_cast<float4 *>(p.dk + gbase + i) = make_float4(0.f, 0.f, 0.f, 0.f);
                 *reinterpret_cast<float4 *>(p.dv + gbase + i) = make_float4(0.f, 0.f, 0.f, 0.f);
             }

@@ -143,7 +143,7 @@ class Tensor:
         query, key, value = inputs[0], inputs[1], inputs[2]
         saved = getattr(self, "_saved", None)
         if saved is None:
-            raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128} and "
+            raise RuntimeError("SDPA backward: built for float16 CUDA tensors with d_k == d_v in {64, 128, 256} and "
                                "implicit (causal / kv_lens) masks; this forward kept no row statistics")
         g = grad if grad.dtype == "float32" else None
         if g is None or g.device != "cuda":

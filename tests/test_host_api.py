@@ -58,7 +58,7 @@ def test_backward_rejects_bad_descriptors_before_any_launch():
     assert lib.tx_sdpa_backward(None) == 1
     d = _lib.SdpaBwdDesc(q=16, k=16, v=16, out=16, dout=16, lse=16, dq=16, dk=16, dv=16, batch=1, q_heads=2,
                          kv_heads=2, seq_q=8, seq_k=8, d=32)
-    assert lib.tx_sdpa_backward(ctypes.byref(d)) == 5 and b"d in {64, 128}" in lib.tx_last_error()
+    assert lib.tx_sdpa_backward(ctypes.byref(d)) == 5 and b"d in {64, 128, 256}" in lib.tx_last_error()
     d.d = 64
     d.kv_heads = 3
     assert lib.tx_sdpa_backward(ctypes.byref(d)) == 1

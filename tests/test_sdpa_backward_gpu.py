@@ -125,6 +125,9 @@ CASES = [
     (2, 2, 2, 384, 384, 128, True, [384, 200]),
     (1, 8, 2, 513, 640, 128, False, [600]),
     (1, 2, 2, 700, 64, 64, True, None),
+    (1, 2, 1, 200, 333, 256, False, None),
+    (2, 4, 2, 300, 300, 256, True, [300, 129]),
+    (1, 1, 1, 1, 1, 256, False, None),
 ]
 
 
@@ -235,8 +238,8 @@ def test_random_shapes_forward_and_backward(seed):
     Hkv = int(rng.integers(1, 4))
     Hq = Hkv * int(rng.integers(1, 4))
     B = int(rng.integers(1, 4))
-    Sq = int(rng.integers(1, 700 if d <= 128 else 300))
-    Sk = int(rng.integers(1, 700 if d <= 128 else 300))
+    Sq = int(rng.integers(1, 700 if d <= 128 else 400))
+    Sk = int(rng.integers(1, 700 if d <= 128 else 400))
     causal = bool(rng.integers(0, 2))
     lens = [int(x) for x in rng.integers(1, Sk + 1, size=B)] if rng.integers(0, 2) else None
     out_f16 = bool(rng.integers(0, 2))
@@ -244,7 +247,7 @@ def test_random_shapes_forward_and_backward(seed):
     k = seeded(3000 + seed, B, Hkv, Sk, d).astype(np.float16)
     v = seeded(4000 + seed, B, Hkv, Sk, d).astype(np.float16)
     ref = oracle.sdpa_structured(widen(q), widen(k), widen(v), causal=causal, kv_lens=lens)
-    if d > 128:
+    if d > 256:
         got, tc = sdpa_device(q, k, v, causal=causal, kv_lens=lens, flags=_lib.TX_SDPA_OUT_F16 if out_f16 else 0)
         assert tc
         assert_close_fp16(got.astype(np.float32), ref)

@@ -245,3 +245,15 @@ def test_section_profile_entry_point():
     assert t[0] > 0 and t[16] > 0 and t[24] > 0                # softmax, MMA and producer lanes all reported
     assert t[5] > t[3] > 0                                     # exponentials cost more than the row max
     assert sum(t[1:9]) <= t[0] * 1.05
+
+
+def test_non_blocking_python_calls_are_stream_ordered():
+    """sync=False returns after the launch; a burst of such calls followed by one synchronize() gives
+    the same bits as blocking calls (each call's temporaries go back to the pool in stream order)."""
+    q, k, v = (seeded(i, 2, 4, 640, 64).astype(np.float16) for i in (110, 111, 112))
+    tq, tk, tv = (ts.Tensor(x, dtype="float16", device="cuda") for x in (q, k, v))
+    blocking = F.scaled_dot_product_attention_ex(tq, tk, tv, causal=True, kv_lens=[640, 333]).numpy()
+    outs = [F.scaled_dot_product_attention_ex(tq, tk, tv, causal=True, kv_lens=[640, 333], sync=False) for _ in range(8)]
+    ts.synchronize()
+    for o in outs:
+        assert np.array_equal(o.numpy().view(np.uint32), blocking.view(np.uint32))
