@@ -17,7 +17,9 @@
 //                        registers -> P^T, dS^T (fp16, TMEM) -> dV += P^T dO, dK += dS^T Q
 //
 // Roles per CTA as in the forward kernel: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner,
-// warps 2-5 one thread per TMEM lane.  Every wait is bounded (ptx::mbar_wait); a wait that runs out
+// then one or two row warpgroups (4 warps each, one thread per TMEM lane; two warpgroups split a
+// tile's columns).  Head dims 64, 128 and 256 (at 256 the dK/dV kernel runs two CTAs per key tile,
+// each accumulating half of the gradient columns).  Every wait is bounded (ptx::mbar_wait); a wait that runs out
 // sets the CTA's abort flag and a code in the device status word.
 #pragma once
 
