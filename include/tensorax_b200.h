@@ -35,7 +35,10 @@ enum {
     TX_ERR_INVALID = 1,    /* bad shape / pointer / dtype combination (reference: std::runtime_error) */
     TX_ERR_NO_DEVICE = 2,  /* no usable CUDA device */
     TX_ERR_CUDA = 3,       /* a CUDA runtime or driver call failed */
-    TX_ERR_KERNEL = 4,     /* a kernel gave up on a bounded wait and reported it */
+    TX_ERR_KERNEL = 4,     /* a kernel gave up on a bounded wait (2 s) and reported it; tx_last_error() names the
+                              stage: 1 misaligned shared memory, 2/3/4 forward producer / MMA / softmax warp,
+                              12/13/14 linear-kernel producer / MMA / split warps, 22/23/24 backward
+                              producer / MMA / row warps */
     TX_ERR_UNSUPPORTED = 5
 };
 

@@ -28,7 +28,7 @@
 
 namespace txb {
 
-enum : int { BWD_ERR_PRODUCER = 12, BWD_ERR_MMA = 13, BWD_ERR_ROWS = 14 };
+enum : int { BWD_ERR_PRODUCER = 22, BWD_ERR_MMA = 23, BWD_ERR_ROWS = 24 };
 
 struct BwdParams {
     const float *lse;         // [B,Hq,Sq] log2-domain row statistic written by the forward
