@@ -760,10 +760,12 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, BWD_ERR_ROWS); }
         if (!run && *abort_flag == 0 && key < p.Sk) {
-            // no query sees these keys: zero gradients
+            // no query sees these keys: zero gradients -- unless the batch element has no valid key at
+            // all, where the forward rows are 0/0 and the reference's rule propagates NaN to every gradient
+            const float fill = kv_limit == 0 ? __int_as_float(0x7fc00000) : 0.f;
             for (int i = 0; i < DA; i += 4) {
-                *reinterpret_cast<float4 *>(p.dk + gbase + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4 *>(p.dv + gbase + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(p.dk + gbase + i) = make_float4(fill, fill, fill, fill);
+                *reinterpret_cast<float4 *>(p.dv + gbase + i) = make_float4(fill, fill, fill, fill);
             }
         }
     }

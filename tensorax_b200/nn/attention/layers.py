@@ -71,10 +71,17 @@ class MultiHeadAttention:
     steps are folded into the projections, which write and read the
     [batch, heads, seq, head_dim] layout directly.  ``dropout`` is stored and never
     applied, as in the reference.
+
+    Additive (no reference counterpart): ``attention_dtype="float16"`` rounds the projected heads to
+    fp16 and runs the attention step on the tensor-core kernel (fp32 accumulation, fp32 result; fp16
+    tolerances instead of fp32 ones); ``forward(..., causal=, kv_lens=)`` take the implicit masks.
     """
 
     def __init__(self, embed_dim: int, num_heads: int, bias: bool = True, dropout: float = 0.0,
-                 device: str = "cpu"):
+                 device: str = "cpu", attention_dtype: str = "float32"):
+        if attention_dtype not in ("float32", "float16"):
+            raise ValueError("attention_dtype must be 'float32' or 'float16'")
+        self.attention_dtype = attention_dtype
         if embed_dim % num_heads != 0:
             raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads})")
         self.embed_dim = embed_dim
@@ -110,7 +117,8 @@ class MultiHeadAttention:
             return F.scaled_dot_product_attention_ex(q, k, v, mask, causal=causal, kv_lens=kv_lens)
         return F.scaled_dot_product_attention(q, k, v, mask)
 
-    def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
+    def forward(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None, causal: bool = False,
+                kv_lens=None) -> Tensor:
         """query (batch, seq_q, embed_dim); key, value (batch, seq_k, embed_dim); mask optional
         (batch, num_heads, seq_q, seq_k).  Returns (batch, seq_q, embed_dim)."""
         from ... import _C
@@ -124,14 +132,17 @@ class MultiHeadAttention:
         q = project(query, "q_weight", "q_bias")          # (batch, heads, seq, head_dim), no transpose pass
         k = project(key, "k_weight", "k_bias")
         v = project(value, "v_weight", "v_bias")
-        attn = F.scaled_dot_product_attention(q, k, v, mask)
+        if self.attention_dtype == "float16":
+            q, k, v = F.cast_to_fp16(q), F.cast_to_fp16(k), F.cast_to_fp16(v)
+        attn = self.attend(q, k, v, mask, causal=causal, kv_lens=kv_lens)
         out = _C.linear(attn._c_tensor, P["out_weight"]._c_tensor,
                         P["out_bias"]._c_tensor if P["out_bias"] is not None else None,
                         heads_in=self.num_heads)         # heads merged while reading
         return Tensor._wrap(out)
 
-    def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None) -> Tensor:
-        return self.forward(query, key, value, mask)
+    def __call__(self, query: Tensor, key: Tensor, value: Tensor, mask: Tensor = None, causal: bool = False,
+                 kv_lens=None) -> Tensor:
+        return self.forward(query, key, value, mask, causal=causal, kv_lens=kv_lens)
 
     def __repr__(self) -> str:
         return (f"MultiHeadAttention(embed_dim={self.embed_dim}, num_heads={self.num_heads}, "

@@ -90,3 +90,25 @@ def test_multi_head_attention_forward_with_mask_and_no_bias():
     got = mha(xt, xt, xt, ts.Tensor(mask, device="cuda")).numpy()
     ref = oracle.mha_forward_f32(x, x, x, params, H, mask)
     assert_close_fp32(got, ref, atol=2e-5)     # four chained fp32 stages
+
+
+def test_multi_head_attention_with_fp16_attention_step_and_implicit_causal_mask():
+    """attention_dtype='float16': projections in fp32, heads rounded to fp16, attention on the tensor-core
+    kernel (head_dim 64), output projection in fp32; causal= instead of the dense mask.  Against the fp32
+    composition of the reference's CPU ops with the dense causal mask, at the fp16 tolerance."""
+    from conftest import assert_close_fp16
+    B, S, E, H = 2, 300, 256, 4
+    mha = MultiHeadAttention(E, H, attention_dtype="float16").cuda()
+    params = {n: p.numpy() for n, p in mha._parameters.items() if p is not None}
+    x = seeded(9, B, S, E)
+    mask = np.where(np.tril(np.ones((S, S), bool)), 0.0, -np.inf).astype(np.float32)
+    mask = np.ascontiguousarray(np.broadcast_to(mask, (B, H, S, S)))
+    xt = ts.Tensor(x, device="cuda")
+    got = mha(xt, xt, xt, causal=True).numpy()
+    ref = oracle.mha_forward_f32(x, x, x, params, H, mask)
+    assert_close_fp16(got, ref)
+    same = MultiHeadAttention(E, H).cuda()
+    same._parameters = mha._parameters
+    assert_close_fp32(same(xt, xt, xt, causal=True).numpy(), ref, atol=2e-5)   # fp32 path, implicit mask
+    with pytest.raises(ValueError):
+        MultiHeadAttention(E, H, attention_dtype="bfloat16")

@@ -258,3 +258,19 @@ def test_random_shapes_forward_and_backward(seed):
     rq, rk, rv, _ = oracle.sdpa_backward(widen(q), widen(k), widen(v), g, causal=causal, kv_lens=lens)
     for got, r, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
         assert_grad_close(got, r, f"{name} {(B, Hq, Hkv, Sq, Sk, d, causal, lens, out_f16)}")
+
+
+def test_batch_element_without_valid_keys_propagates_nan_like_the_reference_rule():
+    """kv_lens[b] = 0: the forward rows of that batch element are 0/0 (NaN, as the reference), and the
+    autograd rule (tensorax/tensor.py:806-827) then yields NaN for all of its gradients; the other batch
+    elements are unaffected."""
+    B, Hq, Hkv, S, d = 2, 2, 1, 200, 64
+    q, k, v = (seeded(i, B, h, S, d).astype(np.float16) for i, h in ((120, Hq), (121, Hkv), (122, Hkv)))
+    g = seeded(123, B, Hq, S, d).astype(np.float32)
+    out, lse, dq, dk, dv = backward_device(q, k, v, g, kv_lens=[0, 150])
+    with np.errstate(all="ignore"):
+        rq, rk, rv, _ = oracle.sdpa_backward(widen(q), widen(k), widen(v), g, kv_lens=[0, 150])
+    assert np.isnan(rq[0]).all() and np.isnan(rk[0]).all() and np.isnan(rv[0]).all()
+    assert np.isnan(out[0]).all() and np.isnan(dq[0]).all() and np.isnan(dk[0]).all() and np.isnan(dv[0]).all()
+    for got, ref, name in ((dq[1:], rq[1:], "dq"), (dk[1:], rk[1:], "dk"), (dv[1:], rv[1:], "dv")):
+        assert_grad_close(got, ref, name)
