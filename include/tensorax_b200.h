@@ -49,6 +49,10 @@ enum {
     TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
     TX_SDPA_OUT_F16 = 4,     /* `out` is fp16 [batch, q_heads, seq_q, d_v] instead of fp32 (the reference only has fp32
                                 output, csrc/tensor_ops.cpp:1062; halves the result's bytes) */
+    TX_SDPA_F32_VIA_F16 = 8, /* fp32 q/k/v: round them to fp16 on the device (pool temporaries, stream-ordered) and run the
+                                tensor-core kernel where its shapes apply -- what the reference's `_mma` variant does inside
+                                its kernel (fp32 in/out, fp16 MMA operands, csrc/cuda/kernels/attn.cu:441-603); fp16
+                                tolerances then apply.  Without the flag fp32 inputs always get exact fp32 arithmetic. */
     TX_SDPA_P_IN_SMEM = 2    /* tensor-core kernel: stage P in shared memory instead of tensor memory
                                 (ignored for d = 512, where shared memory has no room for it) */
 };

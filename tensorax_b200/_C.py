@@ -361,12 +361,16 @@ def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
 
 
 def scaled_dot_product_attention_ex(query, key, value, mask=None, causal=False, kv_lens=None,
-                                    flags=0, out_dtype="float32", want_lse=False, sync=True):
+                                    flags=0, out_dtype="float32", want_lse=False, sync=True, fp16_compute=False):
     """No reference counterpart: implicit masks for sizes where the dense
     [B,H,Sq,Sk] mask cannot exist.  ``causal``: key j visible to query i iff
     j <= i; ``kv_lens``: per-batch count of valid keys; ``out_dtype``: 'float32'
     (what every reference entry returns) or 'float16' (half the result bytes); ``sync=False``: return
     right after the launch (the reference's launchers end in cudaDeviceSynchronize, csrc/cuda/kernels/attn.cu:1519-1520);
-    call ``synchronize()`` before reading the result on the host -- device-side consumers need nothing."""
+    call ``synchronize()`` before reading the result on the host -- device-side consumers need nothing;
+    ``fp16_compute=True``: float32 inputs are rounded to fp16 on the device and run on the tensor cores
+    (what the reference's ``_mma`` variant does inside its kernel, csrc/cuda/kernels/attn.cu:441-603)."""
+    if fp16_compute:
+        flags = int(flags) | _lib.TX_SDPA_F32_VIA_F16
     return _forward(query, key, value, mask, causal=causal, kv_lens=kv_lens, flags=flags, out_dtype=out_dtype,
                     want_lse=want_lse, sync=sync)

@@ -19,6 +19,7 @@ TX_DTYPE_F16 = 1
 TX_SDPA_FORCE_SIMT = 1
 TX_SDPA_P_IN_SMEM = 2
 TX_SDPA_OUT_F16 = 4
+TX_SDPA_F32_VIA_F16 = 8
 
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (

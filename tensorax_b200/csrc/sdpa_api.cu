@@ -292,11 +292,51 @@ int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __
     return TX_OK;
 }
 
+__global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n);
+size_t align_up(size_t x, size_t a);
+
+// fp32 inputs through the tensor-core kernel: fp16 copies of Q, K, V in stream-ordered pool memory.
+int forward_f32_via_f16(const tx_sdpa_desc *d, cudaStream_t st)
+{
+    const int64_t nq = d->batch * d->q_heads * d->seq_q * d->d_k, nk = d->batch * d->kv_heads * d->seq_k * d->d_k,
+                  nv = d->batch * d->kv_heads * d->seq_k * d->d_v;
+    const size_t oq = 0, ok = align_up((size_t)nq * 2, 256), ov = ok + align_up((size_t)nk * 2, 256);
+    char *ws = nullptr;
+    TX_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&ws), ov + (size_t)nv * 2, st));
+    const void *src[3] = {d->q, d->k, d->v};
+    const int64_t n[3] = {nq, nk, nv};
+    const size_t off[3] = {oq, ok, ov};
+    int rc = TX_OK;
+    for (int i = 0; i < 3 && rc == TX_OK; ++i) {
+        const int64_t blocks = (n[i] + 1023) / 1024;
+        if (blocks > 0x7fffffffLL) { rc = fail(TX_ERR_UNSUPPORTED, "SDPA: tensor too large"); break; }
+        cast_f32_to_f16_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const float *>(src[i]),
+                                                               reinterpret_cast<__half *>(ws + off[i]), n[i]);
+        g_launches++;
+        if (cudaGetLastError() != cudaSuccess) rc = fail(TX_ERR_CUDA, "SDPA: cast launch failed");
+    }
+    if (rc == TX_OK) {
+        tx_sdpa_desc h = *d;
+        h.q = ws + oq; h.k = ws + ok; h.v = ws + ov;
+        h.dtype = TX_DTYPE_F16;
+        int *status = nullptr;
+        rc = status_word(&status);
+        if (rc == TX_OK) rc = launch_tc(&h, st, status);
+    }
+    (void)cudaFreeAsync(ws, st);
+    return rc;
+}
+
 int forward(const tx_sdpa_desc *d)
 {
     if (int rc = validate(d)) return rc;
     if (int rc = ensure_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(d->stream);
+    if (d->dtype == TX_DTYPE_F32 && (d->flags & TX_SDPA_F32_VIA_F16)) {
+        tx_sdpa_desc probe = *d;
+        probe.dtype = TX_DTYPE_F16;                 // would the fp16 form of this call run on the tensor cores?
+        if (tc_eligible(&probe)) return forward_f32_via_f16(d, st);
+    }
     if (tc_eligible(d)) {
         int *status = nullptr;
         if (int rc = status_word(&status)) return rc;
@@ -815,6 +855,11 @@ int tx_sdpa_finish(void *stream) { return finish(static_cast<cudaStream_t>(strea
 int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc)
 {
     if (validate(desc) != TX_OK) return 0;
+    if (desc->dtype == TX_DTYPE_F32 && (desc->flags & TX_SDPA_F32_VIA_F16)) {
+        tx_sdpa_desc probe = *desc;
+        probe.dtype = TX_DTYPE_F16;
+        return tc_eligible(&probe) ? 1 : 0;
+    }
     return tc_eligible(desc) ? 1 : 0;
 }
 

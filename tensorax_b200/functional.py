@@ -127,14 +127,17 @@ def scaled_dot_product_attention_mma_fp16(query: Tensor, key: Tensor, value: Ten
 def scaled_dot_product_attention_ex(query: Tensor, key: Tensor, value: Tensor,
                                     mask: Optional[Tensor] = None, causal: bool = False,
                                     kv_lens: Optional[Sequence[int]] = None,
-                                    out_dtype: str = "float32", sync: bool = True) -> Tensor:
+                                    out_dtype: str = "float32", sync: bool = True,
+                                    fp16_compute: bool = False) -> Tensor:
     """No reference counterpart.  Implicit masks for shapes where the reference's
     dense [B,H,Sq,Sk] masks cannot be built: ``causal`` (key j visible to query i
     iff j <= i, what create_causal_mask encodes) and ``kv_lens`` (per-batch valid
     key count, what create_padding_mask encodes).  K/V may have fewer heads than Q.
     ``out_dtype='float16'`` returns a float16 tensor (the reference's fp16 entry always
     returns float32, tensorax/functional.py:397).  ``sync=False`` returns right after the launch;
-    ``tensorax_b200.synchronize()`` (or any download of the result) waits for it."""
+    ``tensorax_b200.synchronize()`` (or any download of the result) waits for it.
+    ``fp16_compute=True``: float32 tensors are rounded to fp16 on the device and attended on the
+    tensor cores (fp32 accumulation and result), as the reference's ``_mma`` variant does internally."""
     _check(query, key, value, mask, _MSG4D)
     if not _C:
         raise RuntimeError("C++ backend not available.")
@@ -143,7 +146,7 @@ def scaled_dot_product_attention_ex(query: Tensor, key: Tensor, value: Tensor,
     if needs_grad and _C.sdpa_backward_supported(query._c_tensor, key._c_tensor, value._c_tensor, mask_c):
         return _with_saved_stats(query, key, value, mask, causal, kv_lens, out_dtype)
     c = _C.scaled_dot_product_attention_ex(query._c_tensor, key._c_tensor, value._c_tensor, mask_c, causal=causal,
-                                           kv_lens=kv_lens, out_dtype=out_dtype, sync=sync)
+                                           kv_lens=kv_lens, out_dtype=out_dtype, sync=sync, fp16_compute=fp16_compute)
     if needs_grad:
         return _result(c, True, ("scaled_dot_product_attention", query, key, value, mask))
     return _result(c)

@@ -257,3 +257,23 @@ def test_non_blocking_python_calls_are_stream_ordered():
     ts.synchronize()
     for o in outs:
         assert np.array_equal(o.numpy().view(np.uint32), blocking.view(np.uint32))
+
+
+def test_fp32_tensors_on_the_tensor_cores_by_request():
+    """TX_SDPA_F32_VIA_F16 / fp16_compute=True: fp32 inputs, operands rounded to fp16 on the device, tensor-core
+    kernel, fp32 result -- equal to running the fp16-rounded inputs through the fp16 path, bit for bit; without
+    the flag the same call keeps exact fp32 arithmetic."""
+    from conftest import assert_close_fp32
+    q, k, v = (seeded(i, 2, 4, 384, 128) for i in (130, 131, 132))
+    via, tc_flagged = sdpa_device(q, k, v, causal=True, flags=_lib.TX_SDPA_F32_VIA_F16)
+    direct, tc = sdpa_device(q.astype(np.float16), k.astype(np.float16), v.astype(np.float16), causal=True)
+    assert tc and tc_flagged and np.array_equal(via.view(np.uint32), direct.view(np.uint32))
+    exact, _ = sdpa_device(q, k, v, causal=True)
+    assert_close_fp32(exact, oracle.sdpa_structured(q, k, v, causal=True))
+    tq, tk, tv = (ts.Tensor(x, device="cuda") for x in (q, k, v))
+    out = F.scaled_dot_product_attention_ex(tq, tk, tv, causal=True, fp16_compute=True)
+    assert out.dtype == "float32" and np.array_equal(out.numpy().view(np.uint32), direct.view(np.uint32))
+    # shapes the tensor-core kernel does not take keep exact fp32 arithmetic even with the flag
+    q2, k2, v2 = (seeded(i, 1, 2, 50, 40) for i in (133, 134, 135))
+    got, _ = sdpa_device(q2, k2, v2, flags=_lib.TX_SDPA_F32_VIA_F16)
+    assert_close_fp32(got, oracle.sdpa_f32(q2, k2, v2))
