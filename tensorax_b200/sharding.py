@@ -74,3 +74,16 @@ def place_output(shard: Shard, full_out, local_out) -> None:
     B, Hq, Sq, dv = full_out.shape
     flat = full_out.reshape(B * Hq, Sq, dv)
     flat[shard.q_head_begin:shard.q_head_end] = local_out.reshape(-1, Sq, dv)
+
+
+def shard_grad(shard: Shard, grad):
+    """View of this rank's slab of the upstream gradient [B, Hq, Sq, d_v] as [n, group, Sq, d_v]
+    (the backward pass shards exactly like the forward: a unit's dK / dV sum only over its own query heads)."""
+    B, Hq, Sq, dv = grad.shape
+    return grad.reshape(-1, shard.group, Sq, dv)[shard.unit_begin:shard.unit_end]
+
+
+def place_kv_grad(shard: Shard, full_grad, local_grad) -> None:
+    """Write a rank's [n, 1, Sk, d] dK or dV into the full [B, Hkv, Sk, d] array."""
+    B, Hkv, Sk, d = full_grad.shape
+    full_grad.reshape(B * Hkv, Sk, d)[shard.unit_begin:shard.unit_end] = local_grad.reshape(-1, Sk, d)

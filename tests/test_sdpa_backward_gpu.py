@@ -220,11 +220,10 @@ def test_sharded_backward_equals_the_single_device_run_bitwise():
         for r in range(world):
             sh = sharding.partition(B, Hkv, Hq, world, r)
             qs, ks, vs, ls = sharding.shard_arrays(sh, q, k, v, lens)
-            gs = g.reshape(B * Hkv, sh.group, S, d)[sh.unit_begin:sh.unit_end]
-            _, _, lq, lk, lv = backward_device(qs, ks, vs, gs, causal=True, kv_lens=ls)
+            _, _, lq, lk, lv = backward_device(qs, ks, vs, sharding.shard_grad(sh, g), causal=True, kv_lens=ls)
             sharding.place_output(sh, dq, lq)
-            dk.reshape(B * Hkv, S, d)[sh.unit_begin:sh.unit_end] = lk.reshape(-1, S, d)
-            dv.reshape(B * Hkv, S, d)[sh.unit_begin:sh.unit_end] = lv.reshape(-1, S, d)
+            sharding.place_kv_grad(sh, dk, lk)
+            sharding.place_kv_grad(sh, dv, lv)
         for a, b in ((dq, fq), (dk, fk), (dv, fv)):
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 

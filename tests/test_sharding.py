@@ -44,6 +44,23 @@ def test_sharded_evaluation_equals_unsharded():
         assert np.array_equal(out.view(np.uint32), full.view(np.uint32))
 
 
+def test_sharded_backward_equals_unsharded():
+    B, Hq, Hkv, S, d = 3, 4, 2, 24, 8
+    q, k, v, g = seeded(1, B, Hq, S, d), seeded(2, B, Hkv, S, d), seeded(3, B, Hkv, S, d), seeded(4, B, Hq, S, d)
+    lens = [24, 11, 17]
+    fq, fk, fv, _ = oracle.sdpa_backward(q, k, v, g, causal=True, kv_lens=lens)
+    for world in (2, 3):
+        dq, dk, dv = (np.full(x.shape, np.nan) for x in (fq, fk, fv))
+        for r in range(world):
+            sh = sharding.partition(B, Hkv, Hq, world, r)
+            qs, ks, vs, ls = sharding.shard_arrays(sh, q, k, v, lens)
+            lq, lk, lv, _ = oracle.sdpa_backward(qs, ks, vs, sharding.shard_grad(sh, g), causal=True, kv_lens=ls)
+            sharding.place_output(sh, dq, lq)
+            sharding.place_kv_grad(sh, dk, lk)
+            sharding.place_kv_grad(sh, dv, lv)
+        assert np.array_equal(dq, fq) and np.array_equal(dk, fk) and np.array_equal(dv, fv)
+
+
 _WORKER = r"""
 import os, sys
 sys.path.insert(0, os.environ["TX_ROOT"]); sys.path.insert(0, os.path.join(os.environ["TX_ROOT"], "tests"))
