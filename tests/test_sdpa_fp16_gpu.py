@@ -215,6 +215,14 @@ def test_host_buffer_entry_point():
         _lib.check(_lib.load().tx_sdpa_forward_host(ctypes.byref(desc)))
         dev, _ = sdpa_device(q, k, v, causal=True, kv_lens=lens)
         assert np.array_equal(out.view(np.uint32), dev.view(np.uint32))
+    # fp16 result through the host form: half the bytes come back
+    out16 = np.empty((B, Hq, S, d), np.float16)
+    desc.out, desc.flags = p(out16), _lib.TX_SDPA_OUT_F16
+    _lib.check(_lib.load().tx_sdpa_forward_host(ctypes.byref(desc)))
+    assert np.array_equal(out16, dev.astype(np.float16))
+    lse = np.empty((B, Hq, S), np.float32)
+    desc.lse = p(lse)
+    assert _lib.load().tx_sdpa_forward_host(ctypes.byref(desc)) == 5          # TX_ERR_UNSUPPORTED, nothing ran
 
 
 def test_sharded_runs_equal_the_single_device_run_bitwise():
