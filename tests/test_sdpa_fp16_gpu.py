@@ -139,6 +139,18 @@ def test_full_size_configs_sampled_against_oracle(cfg):
         assert np.abs(got[:, :, 0, :] - v0).max() <= 2e-3
 
 
+@pytest.mark.parametrize("cfg", [(4, 8, 256, 512), (2, 4, 1024, 256)])
+def test_remaining_reference_accuracy_configs_in_full(cfg):
+    """The two ACCURACY_CONFIGS of tests/test_sdpa_fp16.py:41-60 that neither the golden file (its first seven)
+    nor the sampled full-size runs cover: every output element against the oracle."""
+    B, H, S, d = cfg
+    rng = np.random.Generator(np.random.PCG64(11))
+    q, k, v = (rng.standard_normal((B, H, S, d), dtype=np.float32).astype(np.float16) for _ in range(3))
+    got, tc = sdpa_device(q, k, v)
+    assert tc
+    assert_close_fp16(got, oracle.sdpa_structured(widen(q), widen(k), widen(v), threads=8))
+
+
 @pytest.mark.parametrize("d", [256, 512])
 def test_config5_large_head_dims(d):
     B, H, S = 4, 8, 4096
