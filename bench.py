@@ -305,6 +305,10 @@ def run_ours(args, rank, world, local_rank, emit):
     achieved = FLOPS_PER_STEP / (kernel_ms * 1e-3) / 1e12
     threads = host_threads()
     cpu_dt, cpu_fl, cpu_kind = cpu_sdpa_sample(2048, threads)
+    # Second ceiling of this shape, for context: one exponential per score on the special-function unit
+    # (16 per clock and SM, 148 SMs) caps d = 64 at 4*d = 256 FLOP per exponential.
+    sm_hz = 1e6 * float((clocks or {}).get("sm_mhz") or 1965.0)
+    sfu_ceiling = 4.0 * D * 16 * 148 * sm_hz / 1e12
     line = {
         "metric": METRIC, "value": per_gpu * world, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
@@ -326,7 +330,8 @@ def run_ours(args, rank, world, local_rank, emit):
                      "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_src,
                      "kernel": "sdpa_tc_kernel<DK=64,DV=64,BN=128,NS=3>", "flops_per_launch": FLOPS_PER_STEP,
                      "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP,
-                     "hbm_gbs_algorithmic": ALG_BYTES_PER_STEP / (kernel_ms * 1e-3) / 1e9},
+                     "hbm_gbs_algorithmic": ALG_BYTES_PER_STEP / (kernel_ms * 1e-3) / 1e9,
+                     "sfu_ceiling_tflops": sfu_ceiling, "frac_of_sfu_ceiling": achieved / sfu_ceiling},
         "cpu_baseline": {"value": cpu_fl / cpu_dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": cpu_kind,
                          "sample": f"{threads} concurrent (b,h) slices x 2048 query rows x all {S} keys "
                                    f"({threads * 2048 / (B * H * S):.4f} of one pass), {cpu_dt:.1f} s"},
