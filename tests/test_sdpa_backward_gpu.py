@@ -273,3 +273,23 @@ def test_batch_element_without_valid_keys_propagates_nan_like_the_reference_rule
     assert np.isnan(out[0]).all() and np.isnan(dq[0]).all() and np.isnan(dk[0]).all() and np.isnan(dv[0]).all()
     for got, ref, name in ((dq[1:], rq[1:], "dq"), (dk[1:], rk[1:], "dk"), (dv[1:], rv[1:], "dv")):
         assert_grad_close(got, ref, name)
+
+
+@pytest.mark.parametrize("d", [64, 128, 256])
+def test_peaked_attention_rows_forward_and_backward(d):
+    """Large logits (softmax close to one-hot, running max growing by far more than the lazy-rescale
+    threshold from tile to tile): the rescale path of the forward and the saved statistics stay exact enough
+    for the gradients."""
+    B, H, S = 1, 2, 520
+    rng = np.random.default_rng(77)
+    q = (3.0 * rng.standard_normal((B, H, S, d))).astype(np.float16)
+    k = (3.0 * rng.standard_normal((B, H, S, d))).astype(np.float16)
+    k[:, :, 300:] *= 2.0                                     # later key tiles carry the larger scores
+    v = rng.standard_normal((B, H, S, d)).astype(np.float16)
+    g = rng.standard_normal((B, H, S, d)).astype(np.float32)
+    out, lse, dq, dk, dv = backward_device(q, k, v, g)
+    assert_close_fp16(out, oracle.sdpa_structured(widen(q), widen(k), widen(v)))
+    rq, rk, rv, rl = oracle.sdpa_backward(widen(q), widen(k), widen(v), g)
+    np.testing.assert_allclose(lse, rl, rtol=2e-5, atol=2e-3)
+    for got, r, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
+        assert_grad_close(got, r, name)
