@@ -245,8 +245,10 @@ int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
         // in tensor memory instead, and K / V are fetched as two independent queues.
         return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, false, 0, 2, true, 128>>(d, st, status);
     case 512:
-        // 496 of 512 tensor-memory columns: S 32 | O 256 | P 16 | first 384 elements of Q 192
-        return launch_tc_t<txb::TcCfg<512, 256, 32, 2, true, false, 0, 2, true, 192>>(d, st, status);
+        // All 512 tensor-memory columns: S 64 | O 256 | P 32 | first 320 elements of Q 160.  Those five Q panels
+        // are staged in the empty K/V ring, so shared memory holds only Q's last three panels (48 KB) beside
+        // two 64-key K stages (128 KB) and one V stage (32 KB): 64-key tiles where 32 fitted before.
+        return launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, false, 0, 1, true, 160, true>>(d, st, status);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
 }
@@ -784,7 +786,7 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
         if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, kPolyMaskD64>>(d, st, status, dev);
         else if (d->d_k == 128) rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
         else if (d->d_k == 256) rc = launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, dev);
-        else rc = launch_tc_t<txb::TcCfg<512, 256, 32, 2, true, true, 0, 2, true, 192>>(d, st, status, dev);
+        else rc = launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, true, 0, 1, true, 160, true>>(d, st, status, dev);
     }
     if (rc == TX_OK) rc = finish(st);
     if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)

@@ -73,8 +73,12 @@ enum TcStatus : int {
 };
 
 template <int DK_, int DV_, int BN_, int NS_, bool P_TMEM_, bool PROF_ = false, int POLY_ = 0, int NSV_ = NS_,
-          bool LD_SPLIT_ = false, int QT_ = 0>
+          bool LD_SPLIT_ = false, int QT_ = 0, bool Q_ALIAS_ = false>
 struct TcCfg {
+    // Q_ALIAS: the Q panels that move to tensor memory are staged in the (still empty) K/V ring instead of
+    // a region of their own; the producer starts the ring only after the copy.  Shared memory then holds
+    // just the tail panels of Q, which is what lets d = 512 use 64-key tiles.
+    static constexpr bool Q_ALIAS = Q_ALIAS_;
     // QT: tensor-memory columns that hold the first 2*QT elements of every Q row (fp16 pairs).
     // The QK^T MMAs over that part take A from tensor memory, so they read only the K tile from
     // shared memory; with narrow key tiles the A read is what the shared-memory port runs out of.
@@ -98,13 +102,16 @@ struct TcCfg {
     static constexpr int THREADS = 64 + 32 * SOFTMAX_WARPS;
     static constexpr int KP = DK / 64;    // 64-column (128-byte) panels per row of Q / K
     static constexpr int VP = DV / 64;    // panels per row of this CTA's V slice
-    static constexpr uint32_t Q_BYTES = BM * DK * 2;
+    static constexpr uint32_t Q_BYTES = BM * DK * 2;          // all of the Q tile (what the TMA loads bring in)
+    static constexpr int QP_TMEM = QT_ / 32;                   // 64-element panels of Q held in tensor memory
+    static constexpr int QP_SKIP = Q_ALIAS_ ? QP_TMEM : 0;     // ... of which this many have no place in the Q region
+    static constexpr uint32_t Q_REGION = (DK / 64 - QP_SKIP) * BM * 128;
     static constexpr uint32_t K_BYTES = BN * DK * 2;       // one K stage
     static constexpr uint32_t V_BYTES = BN * DV * 2;       // one V stage
     static constexpr uint32_t KV_PANEL = BN * 128;         // one 64-column panel of a stage
     static constexpr uint32_t P_BYTES = P_TMEM ? 0 : BM * BN * 2;
     static constexpr uint32_t OFF_Q = 0;
-    static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
+    static constexpr uint32_t OFF_K = OFF_Q + Q_REGION;
     static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
     static constexpr uint32_t OFF_P = OFF_V + NSV * V_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_P + P_BYTES;
@@ -120,6 +127,8 @@ struct TcCfg {
     static constexpr uint32_t COL_Q = BN + DV + (P_TMEM ? BN / 2 : 0);
     static constexpr uint32_t COLS_USED = COL_Q + QT;
     static_assert(QT % 32 == 0 && 2 * QT <= DK, "Q columns in tensor memory come in whole 64-element panels");
+    static_assert(!Q_ALIAS || (QT > 0 && (uint32_t)QP_TMEM * BM * 128 <= NS * K_BYTES + NSV * V_BYTES),
+                  "the staged Q panels must fit in the K/V ring");
     static constexpr uint32_t TMEM_COLS = COLS_USED <= 32 ? 32 : COLS_USED <= 64 ? 64
                                         : COLS_USED <= 128 ? 128 : COLS_USED <= 256 ? 256 : 512;
     static constexpr int CTAS_PER_SM = (SMEM_BYTES <= 115712 && TMEM_COLS <= 256) ? 2 : 1;
@@ -228,11 +237,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 ptx::prefetch_tmap(&tm_v);
                 ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
-                for (int pn = 0; pn < Cfg::KP; ++pn)
-                    ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+                for (int pn = 0; pn < Cfg::KP; ++pn) {
+                    const uint32_t dst = (Cfg::Q_ALIAS && pn < Cfg::QP_TMEM)
+                                             ? k_s + pn * (BM * 128)                           // staged in the ring
+                                             : q_s + (pn - Cfg::QP_SKIP) * (BM * 128);
+                    ptx::tma_load_3d(dst, &tm_q, q_full, pn * 64, q0, bh);
+                }
             }
             __syncwarp();
             bool ok = true;
+            if constexpr (Cfg::Q_ALIAS) ok = ptx::mbar_wait(q_tmem, 0, abort_flag);   // the ring is free once Q has been copied out
             tick_start();
             const long long t_begin = Cfg::PROF ? clock64() : 0;
             if constexpr (Cfg::LD_SPLIT) {
@@ -354,7 +368,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (leader) {
 #pragma unroll
                     for (int kk = 0; kk < DK / 16; ++kk) {
-                        const uint32_t qa = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+                        const uint32_t qa = (((kk >> 2) - (kk * 8 < Cfg::QT ? 0 : Cfg::QP_SKIP)) * (BM * 128) + (kk & 3) * 32) >> 4;
                         const uint32_t kb = ((kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32) >> 4;
                         if (kk * 8 < Cfg::QT)
                             ptx::mma_ts(t_s, t_q + kk * 8, ptx::make_desc(ks_lo + kb, desc_hi), idesc_qk, kk > 0);
@@ -458,7 +472,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll 1
                 for (int pn = 0; pn < Cfg::QT / 32; ++pn) {
                     uint32_t qv[32];
-                    const uint32_t rowaddr = q_s + (uint32_t)pn * (BM * 128) + (uint32_t)r * 128;
+                    const uint32_t rowaddr = (Cfg::Q_ALIAS ? k_s : q_s) + (uint32_t)pn * (BM * 128) + (uint32_t)r * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c)
                         ptx::ld_shared_v4(rowaddr + (uint32_t)((c ^ (r & 7)) << 4), qv[4 * c], qv[4 * c + 1],
