@@ -28,6 +28,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -47,9 +48,19 @@ ALG_BYTES_PER_STEP = B * H * S * D * (2 + 2 + 2 + 4)        # Q,K,V fp16 reads +
 METRIC = "fp16 SDPA fwd TFLOP/s per GPU at B4 H8 S8192 d64; % of B200 dense fp16 peak"
 PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070 Ti Laptop (sm_86)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel: mean of the two
-# launches captured with `ncu --set full` (profiles/sdpa_tc_kernel_config2_d64.md: 137.14 MB, 136.12 MB)
+# launches captured with `ncu --set full` (137.14 MB, 136.12 MB)
 NCU_DRAM_BYTES_PER_LAUNCH = 136_630_000
+KERNEL_NAME = "sdpa_tc_kernel<DK=64,DV=64,BN=128,NS=3>"
+CPU_ROWS_PER_SLICE = 1024     # query rows per concurrent (b,h) slice in both CPU legs
 WORKLOAD = "config2: SDPA fwd fp16 (fp32 accumulate) B=4 H=8 S=8192 d=64 non-causal, no mask"
+
+
+def measured_peaks() -> dict:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except Exception:
+        return {}
 
 
 def measured_peak():
@@ -97,7 +108,7 @@ def run_reference_arm(args, rank, world, emit):
     if rank != 0:
         return
     threads = host_threads()
-    rows = 1024          # per slice and step: threads * 4*1024*8192*64 = threads * 2.15 GFLOP
+    rows = CPU_ROWS_PER_SLICE   # per slice and step: threads * 4*1024*8192*64 = threads * 2.15 GFLOP
     for _ in range(args.warmup):
         cpu_sdpa_sample(min(rows, 128), threads)
     total_t, total_f, kind = 0.0, 0.0, "port"
@@ -177,7 +188,7 @@ class ClockSampler:
             self._stop.set()
             self._thread.join(timeout=2)
             if self.sm:
-                out.update(sm_mhz=statistics.median(self.sm), sm_max_mhz=self.max_mhz,
+                out.update(sm_mhz=statistics.median(self.sm), sm_mhz_min=min(self.sm), sm_max_mhz=self.max_mhz,
                            reasons=sorted(self.reasons), samples=len(self.sm))
             return out
         out["source"] = "nvidia-smi"
@@ -207,14 +218,43 @@ class ClockSampler:
         self.tmp.close()
         os.unlink(self.tmp.name)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_mhz_min=min(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
         return out
 
 
 # ----------------------------------------------------------------------------- our arm
+NOMINAL_FP16_TFLOPS = 2250.0     # B200 dense fp16/bf16 tensor peak the target is quoted against
+
+
+def unit_randn(torch, dev, seed, tensor_id, first_head, n_heads, rows, d, scale, dtype):
+    """[n_heads, rows, d] of N(0,1)*scale, each head from its own (seed, tensor, flattened head) stream,
+    so that a rank holding any slab of a problem holds the same values as one rank holding all of it."""
+    out = torch.empty((n_heads, rows, d), dtype=dtype, device=dev)
+    g = torch.Generator(device=dev)
+    for i in range(n_heads):
+        g.manual_seed((seed * 1_000_003 + tensor_id) * 1_000_003 + first_head + i)
+        x = torch.randn((rows, d), generator=g, device=dev, dtype=torch.float32)
+        out[i] = (x * scale).to(dtype) if scale != 1.0 else x.to(dtype)
+    return out
+
+
+def visible_scores(S, causal, lens, B):
+    """Scores a (batch, head) row block may see, summed over the batch: the algorithmic work of a masked shape."""
+    total = 0
+    for b in range(B):
+        n = int(lens[b]) if lens is not None else S
+        if causal:
+            total += n * (n + 1) // 2 + (S - n) * n
+        else:
+            total += S * n
+    return total
+
+
 def run_ours(args, rank, world, local_rank, emit):
     import torch
     from tensorax_b200 import _lib
+    from tensorax_b200.sharding import partition
 
     lib = _lib.load()
     if not lib.tx_cuda_is_available():
@@ -238,13 +278,13 @@ def run_ours(args, rank, world, local_rank, emit):
     stream = torch.cuda.current_stream(dev)
     sptr = ctypes.c_void_p(stream.cuda_stream)
 
-    def desc_for(qp, kp, vp, op):
-        return _lib.SdpaDesc(q=qp, k=kp, v=vp, mask=None, kv_lens=None, out=op, batch=B, q_heads=H, kv_heads=H,
-                             seq_q=S, seq_k=S, d_k=D, d_v=D, dtype=_lib.TX_DTYPE_F16, causal=0, flags=args.flags,
-                             stream=sptr)
+    def make_desc(qp, kp, vp, op, b, hq, hkv, s, d, causal=0, lens=None, dtype=_lib.TX_DTYPE_F16, flags=0):
+        return _lib.SdpaDesc(q=qp, k=kp, v=vp, mask=None, kv_lens=lens, out=op, batch=b, q_heads=hq, kv_heads=hkv,
+                             seq_q=s, seq_k=s, d_k=d, d_v=d, dtype=dtype, causal=causal, flags=flags, stream=sptr)
 
-    dev_desc = desc_for(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr())
-    host_desc = desc_for(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host_out.data_ptr())
+    dev_desc = make_desc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, H, S, D, flags=args.flags)
+    host_desc = make_desc(host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host_out.data_ptr(), B, H, H, S, D,
+                          flags=args.flags)
     assert lib.tx_sdpa_uses_tensor_cores(ctypes.byref(dev_desc)) == 1, "config 2 must run on the tcgen05 kernel"
 
     def barrier():
@@ -260,7 +300,24 @@ def run_ours(args, rank, world, local_rank, emit):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---------------- device-resident timing
+    def time_launches(launch, steps, warmup=3):
+        """Mean device time (ms) of `steps` calls of `launch`, CUDA events on the launching stream,
+        L2 flushed before each."""
+        for _ in range(warmup):
+            launch()
+        _lib.check(lib.tx_sdpa_finish(sptr))
+        st = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        en = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            flush.fill_(i & 0xFF)
+            st[i].record(stream)
+            launch()
+            en[i].record(stream)
+        _lib.check(lib.tx_sdpa_finish(sptr))
+        ms = [a.elapsed_time(b) for a, b in zip(st, en)]
+        return sum(ms) / len(ms)
+
+    # ---------------- device-resident timing (the headline)
     for _ in range(max(args.warmup, 3)):
         _lib.check(lib.tx_sdpa_forward(ctypes.byref(dev_desc)))
     _lib.check(lib.tx_sdpa_finish(sptr))
@@ -293,6 +350,116 @@ def run_ours(args, rank, world, local_rank, emit):
     e2e_ms = max_over_ranks(e_start.elapsed_time(e_end) / args.steps)
     clocks = sampler.stop() if sampler else None
     checksum = float(host_out[:: max(n // 4096, 1)].double().sum())
+    # the copies of the same schedule with the kernel left out: what the host <-> device path alone takes
+    copy_only_ms = None
+    if hasattr(lib, "tx_sdpa_forward_host_copies_only"):
+        for _ in range(2):
+            _lib.check(lib.tx_sdpa_forward_host_copies_only(ctypes.byref(host_desc)))
+        barrier()
+        c_start, c_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c_start.record(stream)
+        for _ in range(args.steps):
+            _lib.check(lib.tx_sdpa_forward_host_copies_only(ctypes.byref(host_desc)))
+        c_end.record(stream)
+        barrier()
+        copy_only_ms = max_over_ranks(c_start.elapsed_time(c_end) / args.steps)
+
+    # ---------------- sustained: seconds of back-to-back launches of the same pass (rank 0), clocks sampled
+    sustained = None
+    if rank == 0 and args.sustain_s > 0:
+        n_launch = max(int(args.sustain_s / (per_step_ms[0] * 1e-3)), 10)
+        s_sampler = ClockSampler(local_rank)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(n_launch):
+            _lib.check(lib.tx_sdpa_forward(ctypes.byref(dev_desc)))
+        s1.record(stream)
+        _lib.check(lib.tx_sdpa_finish(sptr))
+        s_ms = s0.elapsed_time(s1)
+        s_clk = s_sampler.stop()
+        mp = measured_peaks()
+        s_tf = FLOPS_PER_STEP * n_launch / (s_ms * 1e-3) / 1e12
+        sustained = {"tflops": s_tf, "seconds": s_ms * 1e-3, "launches": n_launch,
+                     "sm_mhz_median": s_clk.get("sm_mhz"), "sm_mhz_min": s_clk.get("sm_mhz_min"),
+                     "reasons": s_clk.get("reasons"), "l2": "not flushed (back to back); working set 160 MiB > L2",
+                     "frac_of_sustained_peak": s_tf / mp["bf16_tflops_sustained"] if mp.get("bf16_tflops_sustained") else None}
+    barrier()
+    del q, k, v, out
+
+    # ---------------- strong scaling: ONE problem cut by (batch, K/V head) units over the ranks
+    def strong_case(name, Bp, Hq, Hkv, Sp, Dp, causal, kv_scale, steps, seed):
+        group = Hq // Hkv
+        sh = partition(Bp, Hkv, Hq, world, rank)
+
+        def build(u0, u1):
+            nu = u1 - u0
+            qq = unit_randn(torch, dev, seed, 0, u0 * group, nu * group, Sp, Dp, 1.0, torch.float16)
+            kk = unit_randn(torch, dev, seed, 1, u0, nu, Sp, Dp, kv_scale, torch.float16)
+            vv = unit_randn(torch, dev, seed, 2, u0, nu, Sp, Dp, kv_scale, torch.float16)
+            oo = torch.empty((nu * group, Sp, Dp), dtype=torch.float32, device=dev)
+            dd = make_desc(qq.data_ptr(), kk.data_ptr(), vv.data_ptr(), oo.data_ptr(), nu, group, 1, Sp, Dp, causal=int(causal))
+            return (qq, kk, vv, oo), dd
+
+        bufs, dd = build(sh.unit_begin, sh.unit_end)
+        barrier()
+        mine = time_launches(lambda: _lib.check(lib.tx_sdpa_forward(ctypes.byref(dd))), steps)
+        barrier()
+        ms_n = max_over_ranks(mine)
+        flops = 4.0 * Hq * Dp * visible_scores(Sp, causal, None, Bp)
+        rec = None
+        if rank == 0:
+            if world > 1:
+                fb, fd = build(0, Bp * Hkv)
+                ms_1 = time_launches(lambda: _lib.check(lib.tx_sdpa_forward(ctypes.byref(fd))), steps)
+                same = bool(torch.equal(fb[3][: sh.n_units * group], bufs[3]))
+                del fb
+            else:
+                ms_1, same = ms_n, True
+            rec = {"problem": f"B={Bp} Hq={Hq} Hkv={Hkv} S={Sp} d={Dp}" + (" causal" if causal else ""),
+                   "units_total": Bp * Hkv, "units_rank0": sh.n_units, "ms": ms_n, "ms_one_gpu": ms_1,
+                   "tflops_algorithmic": flops / (ms_n * 1e-3) / 1e12,
+                   "tflops_one_gpu": flops / (ms_1 * 1e-3) / 1e12,
+                   "efficiency": ms_1 / (world * ms_n), "rank0_slab_bitwise_equal_to_one_gpu_run": same}
+        del bufs
+        barrier()
+        return rec
+
+    strong = None
+    if not args.headline_only:
+        strong = {"config4": strong_case("config4", 8, 32, 8, 8192, 128, True, 0.5, 5, 4),
+                  "config2": strong_case("config2", B, H, H, S, D, False, 1.0, 10, 2)}
+
+    # ---------------- the other BASELINE configs, device-timed on rank 0
+    configs = None
+    if rank == 0 and not args.headline_only:
+        peak_b, _ = measured_peak()
+        configs = {}
+
+        def one(name, Bp, Hq, Hkv, Sp, Dp, causal, scale_all, kv_scale, lens, steps, dtype=torch.float16, seed=11):
+            qq = unit_randn(torch, dev, seed, 0, 0, Bp * Hq, Sp, Dp, scale_all, dtype)
+            kk = unit_randn(torch, dev, seed, 1, 0, Bp * Hkv, Sp, Dp, scale_all * kv_scale, dtype)
+            vv = unit_randn(torch, dev, seed, 2, 0, Bp * Hkv, Sp, Dp, scale_all * kv_scale, dtype)
+            oo = torch.empty((Bp * Hq, Sp, Dp), dtype=torch.float32, device=dev)
+            ll = torch.tensor(lens, dtype=torch.int32, device=dev) if lens is not None else None
+            dd = make_desc(qq.data_ptr(), kk.data_ptr(), vv.data_ptr(), oo.data_ptr(), Bp, Hq, Hkv, Sp, Dp, causal=int(causal),
+                           lens=ll.data_ptr() if ll is not None else None,
+                           dtype=_lib.TX_DTYPE_F16 if dtype == torch.float16 else _lib.TX_DTYPE_F32)
+            t = time_launches(lambda: _lib.check(lib.tx_sdpa_forward(ctypes.byref(dd))), steps)
+            alg = 4.0 * Hq * Dp * visible_scores(Sp, causal, lens, Bp)
+            dense = 4.0 * Bp * Hq * Sp * Sp * Dp
+            configs[name] = {"ms": t, "tflops_algorithmic": alg / (t * 1e-3) / 1e12,
+                             "tflops_dense_equivalent": dense / (t * 1e-3) / 1e12,
+                             "frac_of_measured_peak": alg / (t * 1e-3) / 1e12 / peak_b,
+                             "tensor_cores": bool(lib.tx_sdpa_uses_tensor_cores(ctypes.byref(dd)))}
+
+        lens3 = np.random.Generator(np.random.PCG64(3)).integers(2048, 4097, size=4).tolist()
+        one("c3", 4, 16, 16, 4096, 128, True, 1.0, 1.0, lens3, 10)
+        configs["c3"]["kv_lens"] = lens3
+        one("c4", 8, 32, 8, 8192, 128, True, 1.0, 0.5, None, 5)
+        one("c5_d256", 4, 8, 8, 4096, 256, False, 1.0 / 16.0, 1.0, None, 10)
+        one("c5_d512", 4, 8, 8, 4096, 512, False, 1.0 / math.sqrt(512.0), 1.0, None, 10)
+        one("fp32_mha_shape", 4, 16, 16, 4096, 128, True, 1.0, 1.0, None, 3, dtype=torch.float32)
+    barrier()
 
     if rank != 0:
         if dist is not None:
@@ -304,7 +471,7 @@ def run_ours(args, rank, world, local_rank, emit):
     kernel_ms = sum(per_step_ms) / len(per_step_ms)           # rank 0's own launches
     achieved = FLOPS_PER_STEP / (kernel_ms * 1e-3) / 1e12
     threads = host_threads()
-    cpu_dt, cpu_fl, cpu_kind = cpu_sdpa_sample(2048, threads)
+    cpu_dt, cpu_fl, cpu_kind = cpu_sdpa_sample(CPU_ROWS_PER_SLICE, threads)
     # Second ceiling of this shape, for context: one exponential per score on the special-function unit
     # (16 per clock and SM, 148 SMs) caps d = 64 at 4*d = 256 FLOP per exponential.
     sm_hz = 1e6 * float((clocks or {}).get("sm_mhz") or 1965.0)
@@ -319,22 +486,32 @@ def run_ours(args, rank, world, local_rank, emit):
                    "parallelism": f"{world} rank(s) x 32 (batch,head) units each, no collective",
                    "l2": "flushed between steps (256 MB write); inputs+output 160 MiB > 126 MB L2",
                    "p_operand": "shared memory" if args.flags & 2 else "tensor memory"},
-        "per_gpu_tflops": per_gpu, "pct_of_peak": 100.0 * per_gpu / peak,
+        "per_gpu_tflops": per_gpu,
+        "pct_of_measured_peak": 100.0 * per_gpu / peak,
+        "pct_of_nominal_peak": 100.0 * per_gpu / NOMINAL_FP16_TFLOPS,
+        "target": {"text": "60 % of B200 dense fp16 tensor peak at this config",
+                   "met_vs_measured_peak": bool(per_gpu / peak >= 0.60),
+                   "met_vs_nominal_peak": bool(per_gpu / NOMINAL_FP16_TFLOPS >= 0.60)},
         "vs_baseline_note": "published number is the reference kernel on an RTX 3070 Ti Laptop (README.md:80-82)",
         "e2e": {"value": world * FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "ms_per_step": e2e_ms, "h2d_bytes_per_step": 3 * n * 2, "d2h_bytes_per_step": n * 4,
+                "ms_per_step": e2e_ms, "copy_only_ms": copy_only_ms,
+                "h2d_bytes_per_step": 3 * n * 2, "d2h_bytes_per_step": n * 4,
                 "api": "tx_sdpa_forward_host (pinned host buffers)", "checksum": checksum},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_src,
-                     "kernel": "sdpa_tc_kernel<DK=64,DV=64,BN=128,NS=3>", "flops_per_launch": FLOPS_PER_STEP,
+                     "frac": achieved / peak, "frac_of_nominal_2250": achieved / NOMINAL_FP16_TFLOPS,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_src,
+                     "kernel": KERNEL_NAME, "flops_per_launch": FLOPS_PER_STEP,
                      "algorithmic_bytes_per_launch": ALG_BYTES_PER_STEP,
                      "hbm_gbs_algorithmic": ALG_BYTES_PER_STEP / (kernel_ms * 1e-3) / 1e9,
                      "sfu_ceiling_tflops": sfu_ceiling, "frac_of_sfu_ceiling": achieved / sfu_ceiling},
+        "sustained": sustained,
+        "strong": strong,
+        "configs": configs,
         "cpu_baseline": {"value": cpu_fl / cpu_dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": cpu_kind,
-                         "sample": f"{threads} concurrent (b,h) slices x 2048 query rows x all {S} keys "
-                                   f"({threads * 2048 / (B * H * S):.4f} of one pass), {cpu_dt:.1f} s"},
+                         "sample": f"{threads} concurrent (b,h) slices x {CPU_ROWS_PER_SLICE} query rows x all {S} keys "
+                                   f"({threads * CPU_ROWS_PER_SLICE / (B * H * S):.4f} of one pass), {cpu_dt:.1f} s"},
     }
     emit(line)
     if dist is not None:
@@ -358,6 +535,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sustain-s", type=float, default=2.0,
+                    help="seconds of back-to-back launches for the sustained figure (0 = skip)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the strong-scaling cases and the other BASELINE configs (for profiler captures)")
     ap.add_argument("--flags", type=int, default=int(os.environ.get("TX_BENCH_FLAGS", "0")),
                     help="TX_SDPA_* flags passed to the kernel selection (2 = stage P in shared memory)")
     args = ap.parse_args()

@@ -168,6 +168,34 @@ TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
 /* How many kernels of this library have been launched by this process so far. */
 TX_API int64_t tx_kernel_launch_count(void);
 
+/* ---- section profiles of the fp32 launchers: reference csrc/tensor_ops.h:214-233
+ *      (sdpa_{naive,tiled,flash,mma,optimized_flash}_profile_sections_cuda, bound to Python as
+ *      profile_sections_sdpa_{naive,tiled,flash,mma,flash_optimized}, csrc/tensor_ops.cpp:1434-1507,1622-1636).
+ *      Same pointers and sizes as the launcher of the same name; `ticks32` receives 32 clock64 stamps of
+ *      thread 0 of CTA (0,0,0) of one instrumented launch (consecutive differences = section times, as with
+ *      TX_TICK, csrc/cuda/profiling.cuh:20-51): [0] kernel entry, [1] first Q/K chunk staged, and for the
+ *      first key tile [2] QK^T accumulated, [3] scores scaled/masked/parked, [4] online softmax done,
+ *      [5] O updated; [6] all key tiles done, [7] output written; the rest stay 0.  All five names run the
+ *      one exact-fp32 kernel, so they report the same sections.  Each call is also an NVTX range
+ *      ("sdpa.naive.profile", ...; the launchers themselves are "sdpa.naive", ..., "sdpa.mma.fp16"), as in
+ *      the reference (csrc/cuda/profiling.cuh:7-18, csrc/cuda/kernels/attn.cu:973-1701). */
+TX_API int tx_sdpa_naive_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                                               float *out, int64_t batch_size, int64_t num_heads, int64_t seq_len_q,
+                                               int64_t seq_len_k, int64_t d_k, int64_t d_v, long long *ticks32);
+TX_API int tx_sdpa_tiled_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                                               float *out, int64_t batch_size, int64_t num_heads, int64_t seq_len_q,
+                                               int64_t seq_len_k, int64_t d_k, int64_t d_v, long long *ticks32);
+TX_API int tx_sdpa_flash_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                                               float *out, int64_t batch_size, int64_t num_heads, int64_t seq_len_q,
+                                               int64_t seq_len_k, int64_t d_k, int64_t d_v, long long *ticks32);
+TX_API int tx_sdpa_mma_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask,
+                                             float *out, int64_t batch_size, int64_t num_heads, int64_t seq_len_q,
+                                             int64_t seq_len_k, int64_t d_k, int64_t d_v, long long *ticks32);
+TX_API int tx_sdpa_optimized_flash_profile_sections_cuda(const float *Q, const float *K, const float *V,
+                                                         const float *mask, float *out, int64_t batch_size,
+                                                         int64_t num_heads, int64_t seq_len_q, int64_t seq_len_k,
+                                                         int64_t d_k, int64_t d_v, long long *ticks32);
+
 /* ---- section profile: reference csrc/tensor_ops.cpp:1434-1507 (profile_sections_sdpa_*) over the
  *      TX_TICK clock64 sections of csrc/cuda/profiling.cuh:20-51.  Runs `desc` once on an instrumented
  *      build of the tensor-core kernel (d = 64 or 128) and returns 32 cycle counters of CTA (0,0,0),

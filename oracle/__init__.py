@@ -28,13 +28,26 @@ _i64 = ctypes.c_int64
 _fp = ctypes.c_void_p
 
 
-def build(with_ref: bool | None = None, ref_root: str = "/root/reference") -> None:
+def reference_root() -> str | None:
+    """Where the reference checkout lies: $TENSORAX_REF, else a directory named `reference` beside this
+    repository.  None when neither holds the reference's CPU source."""
+    cands = [os.environ.get("TENSORAX_REF"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "csrc", "cpu", "tensor_cpu.cpp")):
+            return c
+    return None
+
+
+def build(with_ref: bool | None = None, ref_root: str | None = None) -> None:
     """Compile the checkers.  ``with_ref=None`` builds the reference copy only
     when the reference checkout is present on this machine."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
+    ref_root = ref_root or reference_root()
     if with_ref is None:
-        with_ref = os.path.isfile(os.path.join(ref_root, "csrc", "cpu", "tensor_cpu.cpp"))
+        with_ref = ref_root is not None
     if with_ref:
+        if ref_root is None:
+            raise RuntimeError("reference checkout not found: set TENSORAX_REF")
         subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True,
                        capture_output=True)
 

@@ -33,6 +33,8 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_forward", "tx_sdpa_finish", "tx_sdpa_uses_tensor_cores",
     "tx_kernel_launch_count", "tx_profile_sections_sdpa", "tx_sdpa_forward_host", "tx_sdpa_fp16_static_scratch",
     "tx_sdpa_backward",
+    "tx_sdpa_naive_profile_sections_cuda", "tx_sdpa_tiled_profile_sections_cuda", "tx_sdpa_flash_profile_sections_cuda",
+    "tx_sdpa_mma_profile_sections_cuda", "tx_sdpa_optimized_flash_profile_sections_cuda",
 )
 
 
@@ -94,6 +96,8 @@ def load():
     for name in ("tx_sdpa_naive_cuda", "tx_sdpa_tiled_cuda", "tx_sdpa_flash_cuda",
                  "tx_sdpa_optimized_flash_cuda", "tx_sdpa_mma_cuda"):
         getattr(lib, name).argtypes = f32_sig
+    for name in ("naive", "tiled", "flash", "mma", "optimized_flash"):
+        getattr(lib, f"tx_sdpa_{name}_profile_sections_cuda").argtypes = f32_sig + [ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_sdpa_mma_fp16_cuda.argtypes = [c_void_p] * 4 + [c_int64] * 6
     lib.tx_cast_f32_to_f16_cuda.argtypes = [c_void_p, c_void_p, c_int64]
     lib.tx_repeat_interleave_cuda.argtypes = [c_void_p, c_void_p] + [c_int64] * 4 + [c_int32]

@@ -400,6 +400,14 @@ __device__ __forceinline__ void reg_fence_cols(uint32_t *r)
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---------------------------------------------------------------- register reallocation
+// Executed by every warp of a warpgroup (four consecutive warps, the first a multiple of four):
+// give registers back to the SM's pool / take more from it.  N: multiple of 8 in [24, 256].
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---------------------------------------------------------------- math
 __device__ __forceinline__ float ex2_approx(float x)
 {
@@ -422,6 +430,29 @@ __device__ __forceinline__ float ex2_poly(float x)
     p = fmaf(f, p, 0.9999481439590454f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
 }
+// 2^x for two values at once on the FMA pipe: round to the nearest integer n with the
+// 1.5*2^23 trick, degree-3 polynomial for 2^f on f = x - n in [-0.5, 0.5] (max relative error
+// 1.6e-4, a third of the fp16 rounding P gets anyway), n added into the exponent field.
+// Inputs below -126 (masked scores are -inf) are clamped and come out as ~1e-38, which the
+// fp16 conversion turns into 0.
+__device__ __forceinline__ float2 ex2_poly2(float2 x)
+{
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);
+    const float2 xr = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(xr, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.05360212177038193f, 0.05360212177038193f),
+                          make_float2(0.24237291514873505f, 0.24237291514873505f));
+    p = __ffma2_rn(f, p, make_float2(0.6935023665428162f, 0.6935023665428162f));
+    p = __ffma2_rn(f, p, make_float2(0.9999481439590454f, 0.9999481439590454f));
+    float2 r;
+    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(xr.x) << 23));
+    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(xr.y) << 23));
+    return r;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c)
 {
     float d;

@@ -17,10 +17,23 @@
 #include <string>
 #include <vector>
 
+// NVTX ranges around the entry points, as the reference's launchers have them
+// (csrc/cuda/profiling.cuh:7-18: scoped ranges when the NVTX header is present, nothing otherwise).
+#if defined(__has_include)
+#if __has_include(<nvtx3/nvtx3.hpp>)
+#include <nvtx3/nvtx3.hpp>
+#define TX_NVTX_RANGE(name) ::nvtx3::scoped_range tx_nvtx_range_{(name)}
+#endif
+#endif
+#ifndef TX_NVTX_RANGE
+#define TX_NVTX_RANGE(name) ((void)0)
+#endif
+
 #include "linear_simt.cuh"
 #include "linear_tc.cuh"
 #include "sdpa_simt.cuh"
 #include "sdpa_tc.cuh"
+#include "sdpa_tc_pair.cuh"
 #include "sdpa_bwd.cuh"
 
 namespace {
@@ -168,26 +181,26 @@ bool tc_eligible(const tx_sdpa_desc *d)
 }
 
 // ------------------------------------------------------------------ launches
-template <typename T, int DVC>
+template <typename T, int DVC, bool PROF>
 int launch_simt_t(const txb::SimtParams &p, cudaStream_t st)
 {
     dim3 grid((unsigned)((p.dv + 32 * DVC - 1) / (32 * DVC)),
               (unsigned)((p.Sq + txb::SIMT_BR - 1) / txb::SIMT_BR), (unsigned)(p.B * p.Hq));
-    txb::sdpa_simt_kernel<T, DVC><<<grid, txb::SIMT_THREADS, 0, st>>>(p);
+    txb::sdpa_simt_kernel<T, DVC, PROF><<<grid, txb::SIMT_THREADS, 0, st>>>(p);
     g_launches++;
     TX_CUDA(cudaGetLastError());
     return TX_OK;
 }
 
-template <typename T>
+template <typename T, bool PROF = false>
 int launch_simt(const txb::SimtParams &p, cudaStream_t st)
 {
     if (p.B * p.Hq > 65535) return fail(TX_ERR_UNSUPPORTED, "SDPA: batch*heads > 65535");
     if ((p.Sq + txb::SIMT_BR - 1) / txb::SIMT_BR > 65535) return fail(TX_ERR_UNSUPPORTED, "SDPA: seq_len_q too large");
-    if (p.dv <= 32) return launch_simt_t<T, 1>(p, st);
-    if (p.dv <= 64) return launch_simt_t<T, 2>(p, st);
-    if (p.dv <= 128) return launch_simt_t<T, 4>(p, st);
-    return launch_simt_t<T, 8>(p, st);   // wider heads: one CTA column per 256 value columns
+    if (p.dv <= 32) return launch_simt_t<T, 1, PROF>(p, st);
+    if (p.dv <= 64) return launch_simt_t<T, 2, PROF>(p, st);
+    if (p.dv <= 128) return launch_simt_t<T, 4, PROF>(p, st);
+    return launch_simt_t<T, 8, PROF>(p, st);   // wider heads: one CTA column per 256 value columns
 }
 
 // Elements (bit e = element e of each group of 16) whose exponential is evaluated by the FMA-pipe
@@ -225,20 +238,91 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     return TX_OK;
 }
 
+template <class Cfg>
+int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
+{
+    CUtensorMap tq, tk, tv;
+    if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, d->d_k, Cfg::BM)) return rc;
+    if (int rc = make_map(&tk, d->k, d->batch * d->kv_heads, d->seq_k, d->d_k, Cfg::BN)) return rc;
+    if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, d->d_v, Cfg::BN)) return rc;
+    txb::TcParams p;
+    p.out = d->out;
+    p.out_f16 = (d->flags & TX_SDPA_OUT_F16) ? 1 : 0;
+    p.lse = d->lse;
+    p.kv_lens = d->kv_lens;
+    p.status = status;
+    p.Hq = (int)d->q_heads;
+    p.Hkv = (int)d->kv_heads;
+    p.Sq = (int)d->seq_q;
+    p.Sk = (int)d->seq_k;
+    p.dv_total = (int)d->d_v;
+    p.causal = d->causal ? 1 : 0;
+    p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
+    p.prof = prof;
+    TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg::SMEM_BYTES));
+    dim3 grid((unsigned)((d->seq_q + 2 * Cfg::BM - 1) / (2 * Cfg::BM)), (unsigned)(d->batch * d->q_heads), 1);
+    txb::sdpa_tc_pair_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    g_launches++;
+    TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+// Experiment switch (kernel variant by number) while the d = 64 / 128 shapes are being tuned.
+int variant_env(const char *name)
+{
+    const char *e = std::getenv(name);
+    return e ? std::atoi(e) : -1;
+}
+
+template <bool PROF>
+int launch_variant(int variant, const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof)
+{
+    using namespace txb;
+    switch (variant) {
+    // d = 64, two CTAs per SM, one query tile each
+    case 0: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, kPolyMaskD64>>(d, st, status, prof);
+    case 10: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0003>>(d, st, status, prof);
+    case 11: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0303>>(d, st, status, prof);
+    case 12: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0333>>(d, st, status, prof);
+    // d = 64, one CTA per SM, two query tiles
+    case 1: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 0, 128, false, PROF>>(d, st, status, prof);
+    case 2: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 1, 128, false, PROF>>(d, st, status, prof);
+    case 3: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 1, 96, false, PROF>>(d, st, status, prof);
+    case 4: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 128, false, PROF>>(d, st, status, prof);
+    case 5: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 96, false, PROF>>(d, st, status, prof);
+    case 6: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, 1, 128, false, PROF>>(d, st, status, prof);
+    case 7: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 64, false, PROF>>(d, st, status, prof);
+    case 8: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 0, 128, false, PROF>>(d, st, status, prof);
+    case 9: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, 1, 96, false, PROF>>(d, st, status, prof);
+    // d = 128
+    case 20: return launch_tc_t<TcCfg<128, 128, 64, 2, true, PROF>>(d, st, status, prof);
+    case 21: return launch_pair_t<PairCfg<128, 128, 2, 0, 1, 128, true, PROF>>(d, st, status, prof);
+    case 22: return launch_pair_t<PairCfg<128, 128, 2, 0, 0, 128, true, PROF>>(d, st, status, prof);
+    case 23: return launch_pair_t<PairCfg<128, 64, 4, 0, 1, 64, false, PROF>>(d, st, status, prof);
+    case 24: return launch_pair_t<PairCfg<128, 128, 2, 0x0003, 1, 128, true, PROF>>(d, st, status, prof);
+    case 25: return launch_pair_t<PairCfg<128, 128, 2, 0x0003, 1, 96, true, PROF>>(d, st, status, prof);
+    }
+    return fail(TX_ERR_UNSUPPORTED, "SDPA: unknown kernel variant %d", variant);
+}
+
 // Tile shapes per head dim (template arguments: DK, DV per CTA, keys per tile, ring depth, P in TMEM).
 //   d= 64: 128 keys/tile, two CTAs per SM      d=128: 64 keys/tile, two CTAs per SM
-//   d=256: 64 keys/tile, one CTA per SM        d=512: 32 keys/tile, two CTAs split the value columns
+//   d=256: 64 keys/tile, one CTA per SM        d=512: 64 keys/tile, two CTAs split the value columns
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
     switch (d->d_k) {
-    case 64:
+    case 64: {
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
-        // d = 64 is bound by the special-function pipe: 2 of every 16 exponentials go to the FMA pipe
-        return launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, false, kPolyMaskD64>>(d, st, status);
-    case 128:
+        const int v = variant_env("TX_SDPA_D64_VARIANT");
+        return launch_variant<false>(v >= 0 && v < 20 ? v : 0, d, st, status, nullptr);
+    }
+    case 128: {
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
-        return launch_tc_t<txb::TcCfg<128, 128, 64, 2, true>>(d, st, status);
+        const int v = variant_env("TX_SDPA_D128_VARIANT");
+        return launch_variant<false>(v >= 20 ? v : 20, d, st, status, nullptr);
+    }
     case 256:
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
         // Narrow key tiles make the A (Q) read the busiest user of the shared-memory port: Q lives
@@ -354,6 +438,7 @@ int forward(const tx_sdpa_desc *d)
     p.Sq = d->seq_q; p.Sk = d->seq_k; p.dk = d->d_k; p.dv = d->d_v;
     p.causal = d->causal ? 1 : 0;
     p.scale = 1.0f / std::sqrt((float)d->d_k);
+    p.prof = nullptr;
     return d->dtype == TX_DTYPE_F16 ? launch_simt<__half>(p, st) : launch_simt<float>(p, st);
 }
 
@@ -384,6 +469,39 @@ int sync_f32(const float *Q, const float *K, const float *V, const float *mask, 
     d.dtype = TX_DTYPE_F32;
     if (int rc = forward(&d)) return rc;
     return finish(nullptr);
+}
+
+// The fp32 launchers' section profile: one instrumented launch of the exact-fp32 kernel, 32 clock64
+// stamps of thread 0 of CTA (0,0,0) (txb::SimtStamp; unused entries stay 0), as the reference's
+// sdpa_*_profile_sections_cuda return them (csrc/cuda/kernels/attn.cu:1113-1140,1617-1722).
+int profile_f32(const float *Q, const float *K, const float *V, const float *mask, float *out,
+                int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    if (!ticks32) return fail(TX_ERR_INVALID, "profile_sections: null output");
+    tx_sdpa_desc d;
+    std::memset(&d, 0, sizeof d);
+    d.q = Q; d.k = K; d.v = V; d.mask = mask; d.out = out;
+    d.batch = B; d.q_heads = H; d.kv_heads = H; d.seq_q = Sq; d.seq_k = Sk; d.d_k = dk; d.d_v = dv;
+    d.dtype = TX_DTYPE_F32;
+    if (int rc = validate(&d)) return rc;
+    if (int rc = ensure_device()) return rc;
+    long long *dev = nullptr;
+    TX_CUDA(cudaMalloc(&dev, 32 * sizeof(long long)));
+    int rc = cudaMemset(dev, 0, 32 * sizeof(long long)) == cudaSuccess ? TX_OK : fail(TX_ERR_CUDA, "cudaMemset failed");
+    if (rc == TX_OK) {
+        txb::SimtParams p;
+        p.q = Q; p.k = K; p.v = V; p.mask = mask; p.kv_lens = nullptr; p.out = out; p.out_f16 = 0;
+        p.B = B; p.Hq = H; p.Hkv = H; p.Sq = Sq; p.Sk = Sk; p.dk = dk; p.dv = dv;
+        p.causal = 0;
+        p.scale = 1.0f / std::sqrt((float)dk);
+        p.prof = dev;
+        rc = launch_simt<float, true>(p, nullptr);
+    }
+    if (rc == TX_OK) rc = finish(nullptr);
+    if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        rc = fail(TX_ERR_CUDA, "cudaMemcpy of the section profile failed");
+    (void)cudaFree(dev);
+    return rc;
 }
 
 __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n)
@@ -631,27 +749,32 @@ int tx_host_free_pinned(void *ptr)
 int tx_sdpa_naive_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
                        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.naive");
     return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
 }
 int tx_sdpa_tiled_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
                        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.tiled");
     return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
 }
 int tx_sdpa_flash_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
                        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.flash");
     return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
 }
 int tx_sdpa_optimized_flash_cuda(const float *Q, const float *K, const float *V, const float *mask,
                                  float *out, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk,
                                  int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.flash_optimized");
     return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
 }
 int tx_sdpa_mma_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
                      int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.mma");
     // The reference computes this variant with fp16 operands; the exact-fp32 kernel
     // is used here, which is strictly closer to the CPU path.
     return sync_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv);
@@ -660,6 +783,7 @@ int tx_sdpa_mma_cuda(const float *Q, const float *K, const float *V, const float
 int tx_sdpa_mma_fp16_cuda(const void *Q_h, const void *K_h, const void *V_h, float *out, int64_t B,
                           int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
+    TX_NVTX_RANGE("sdpa.mma.fp16");
     tx_sdpa_desc d;
     std::memset(&d, 0, sizeof d);
     d.q = Q_h; d.k = K_h; d.v = V_h; d.out = out;
@@ -667,6 +791,37 @@ int tx_sdpa_mma_fp16_cuda(const void *Q_h, const void *K_h, const void *V_h, flo
     d.dtype = TX_DTYPE_F16;
     if (int rc = forward(&d)) return rc;
     return finish(nullptr);
+}
+
+int tx_sdpa_naive_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    TX_NVTX_RANGE("sdpa.naive.profile");
+    return profile_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv, ticks32);
+}
+int tx_sdpa_tiled_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    TX_NVTX_RANGE("sdpa.tiled.profile");
+    return profile_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv, ticks32);
+}
+int tx_sdpa_flash_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    TX_NVTX_RANGE("sdpa.flash.profile");
+    return profile_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv, ticks32);
+}
+int tx_sdpa_optimized_flash_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    TX_NVTX_RANGE("sdpa.flash_optimized.profile");
+    return profile_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv, ticks32);
+}
+int tx_sdpa_mma_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask, float *out,
+        int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, long long *ticks32)
+{
+    TX_NVTX_RANGE("sdpa.mma.profile");
+    return profile_f32(Q, K, V, mask, out, B, H, Sq, Sk, dk, dv, ticks32);
 }
 
 int tx_cast_f32_to_f16_cuda(const float *in, void *out, int64_t size)
@@ -766,7 +921,11 @@ int tx_linear_f32_cuda(const float *x, const float *w, const float *bias, float 
     return TX_OK;
 }
 
-int tx_sdpa_forward(const tx_sdpa_desc *desc) { return forward(desc); }
+int tx_sdpa_forward(const tx_sdpa_desc *desc)
+{
+    TX_NVTX_RANGE("sdpa.forward");
+    return forward(desc);
+}
 
 int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
 {
@@ -778,18 +937,24 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     int *status = nullptr;
     if (int rc = status_word(&status)) return rc;
     long long *dev = nullptr;
-    TX_CUDA(cudaMalloc(&dev, 32 * sizeof(long long)));
+    TX_CUDA(cudaMalloc(&dev, 64 * sizeof(long long)));
     cudaStream_t st = static_cast<cudaStream_t>(d->stream);
     int rc = TX_OK;
-    if (cudaMemsetAsync(dev, 0, 32 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
+    if (cudaMemsetAsync(dev, 0, 64 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
     if (rc == TX_OK) {
-        if (d->d_k == 64) rc = launch_tc_t<txb::TcCfg<64, 64, 128, 3, true, true, kPolyMaskD64>>(d, st, status, dev);
-        else if (d->d_k == 128) rc = launch_tc_t<txb::TcCfg<128, 128, 64, 2, true, true>>(d, st, status, dev);
+        if (d->d_k == 64) {
+            const int v = variant_env("TX_SDPA_D64_VARIANT");
+            rc = launch_variant<true>(v >= 0 && v < 20 ? v : 0, d, st, status, dev);
+        } else if (d->d_k == 128) {
+            const int v = variant_env("TX_SDPA_D128_VARIANT");
+            rc = launch_variant<true>(v >= 20 ? v : 20, d, st, status, dev);
+        }
         else if (d->d_k == 256) rc = launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, dev);
         else rc = launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, true, 0, 1, true, 160, true>>(d, st, status, dev);
     }
     if (rc == TX_OK) rc = finish(st);
-    if (rc == TX_OK && cudaMemcpy(ticks32, dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+    const size_t n_ticks = std::getenv("TX_SDPA_PROF64") ? 64 : 32;
+    if (rc == TX_OK && cudaMemcpy(ticks32, dev, n_ticks * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
         rc = fail(TX_ERR_CUDA, "cudaMemcpy of the section profile failed");
     (void)cudaFree(dev);
     return rc;

@@ -37,6 +37,20 @@ struct SimtParams {
     int causal;
     int out_f16;
     float scale;
+    long long *prof;         // optional [32]: clock64 stamps of CTA (0,0,0), thread 0 (PROF instantiation only)
+};
+
+// Stamps of the section profile (the counterpart of TX_TICK, tensorax csrc/cuda/profiling.cuh:20-51):
+// consecutive differences are the time thread 0 of CTA (0,0,0) spent in a section.
+enum SimtStamp : int {
+    SIMT_T_START = 0,        // kernel entry
+    SIMT_T_LOADED = 1,       // first Q / K chunk in shared memory
+    SIMT_T_SCORES = 2,       // first key tile: Q K^T accumulated
+    SIMT_T_PARKED = 3,       // first key tile: scaled, masked, written to shared memory
+    SIMT_T_SOFTMAX = 4,      // first key tile: online softmax done
+    SIMT_T_PV = 5,           // first key tile: O updated
+    SIMT_T_LOOP_END = 6,     // all key tiles done
+    SIMT_T_STORED = 7,       // output written
 };
 
 constexpr int SIMT_BR = 32;    // query rows per CTA
@@ -47,10 +61,17 @@ constexpr int SIMT_THREADS = 256;
 __device__ __forceinline__ float simt_load(const float *p) { return __ldg(p); }
 __device__ __forceinline__ float simt_load(const __half *p) { return __half2float(__ldg(p)); }
 
-template <typename T, int DVC>
+template <typename T, int DVC, bool PROF = false>
 __global__ void __launch_bounds__(SIMT_THREADS)
 sdpa_simt_kernel(const SimtParams p)
 {
+    auto stamp = [&](int i, bool when = true) {
+        if constexpr (PROF) {
+            if (when && p.prof && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+                p.prof[i] = clock64();
+        }
+    };
+    stamp(SIMT_T_START);
     __shared__ float q_s[SIMT_BR][SIMT_DKC + 1];
     __shared__ float k_s[SIMT_BC][SIMT_DKC + 1];
     __shared__ float s_s[SIMT_BR][SIMT_BC + 1];
@@ -105,6 +126,7 @@ sdpa_simt_kernel(const SimtParams p)
                 k_s[r][d] = (key < p.Sk && col < p.dk) ? simt_load(K + key * p.dk + col) : 0.f;
             }
             __syncthreads();
+            stamp(SIMT_T_LOADED, k0 == 0 && d0 == 0);
             const int dmax = (int)min((int64_t)SIMT_DKC, p.dk - d0);
             for (int d = 0; d < dmax; ++d) {
                 const float qa = q_s[sy * 2][d], qb = q_s[sy * 2 + 1][d];
@@ -116,6 +138,7 @@ sdpa_simt_kernel(const SimtParams p)
                 }
             }
         }
+        stamp(SIMT_T_SCORES, k0 == 0);
         // scale, add masks, park the scores
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -132,6 +155,7 @@ sdpa_simt_kernel(const SimtParams p)
             }
         }
         __syncthreads();
+        stamp(SIMT_T_PARKED, k0 == 0);
         // online softmax: warp w owns rows 4w..4w+3, lane covers keys lane, lane+32
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -153,6 +177,7 @@ sdpa_simt_kernel(const SimtParams p)
             if (lane == 0) alpha_s[row_l] = alpha;
         }
         __syncwarp();
+        stamp(SIMT_T_SOFTMAX, k0 == 0);
         // O <- O*alpha + P V for the warp's own 4 rows (only this warp wrote them)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -175,7 +200,9 @@ sdpa_simt_kernel(const SimtParams p)
                 for (int c = 0; c < DVC; ++c) o[r][c] = fmaf(pj, vv[c], o[r][c]);
             }
         }
+        stamp(SIMT_T_PV, k0 == 0);
     }
+    stamp(SIMT_T_LOOP_END);
     if (lane == 0)
 #pragma unroll
         for (int r = 0; r < 4; ++r) l_s[warp * 4 + r] = l_run[r];
@@ -196,6 +223,7 @@ sdpa_simt_kernel(const SimtParams p)
             }
         }
     }
+    stamp(SIMT_T_STORED);
 }
 
 }  // namespace txb

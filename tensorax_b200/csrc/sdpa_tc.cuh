@@ -537,10 +537,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const int e0 = i & 15;
                 const bool pa_x = (Cfg::POLY >> e0) & 1, pa_y = (Cfg::POLY >> (e0 + 1)) & 1;
                 const bool pb_x = (Cfg::POLY >> (e0 + 2)) & 1, pb_y = (Cfg::POLY >> (e0 + 3)) & 1;
-                const float2 ea = make_float2(pa_x ? ptx::ex2_poly(xa.x) : ptx::ex2_approx(xa.x),
-                                              pa_y ? ptx::ex2_poly(xa.y) : ptx::ex2_approx(xa.y));
-                const float2 eb = make_float2(pb_x ? ptx::ex2_poly(xb.x) : ptx::ex2_approx(xb.x),
-                                              pb_y ? ptx::ex2_poly(xb.y) : ptx::ex2_approx(xb.y));
+                // a pair that goes to the polynomial as a whole is evaluated two-wide
+                const float2 ea = (pa_x && pa_y) ? ptx::ex2_poly2(xa)
+                                  : make_float2(pa_x ? ptx::ex2_poly(xa.x) : ptx::ex2_approx(xa.x),
+                                                pa_y ? ptx::ex2_poly(xa.y) : ptx::ex2_approx(xa.y));
+                const float2 eb = (pb_x && pb_y) ? ptx::ex2_poly2(xb)
+                                  : make_float2(pb_x ? ptx::ex2_poly(xb.x) : ptx::ex2_approx(xb.x),
+                                                pb_y ? ptx::ex2_poly(xb.y) : ptx::ex2_approx(xb.y));
                 sum_a = __fadd2_rn(sum_a, ea);
                 sum_b = __fadd2_rn(sum_b, eb);
                 pk[i / 2] = ptx::pack_half2(ea.x, ea.y);

@@ -1,0 +1,531 @@
+// fp16 flash-attention forward for sm_100a, two query tiles per CTA, one CTA per SM.
+//
+// Same arithmetic and the same operand flow as sdpa_tc_kernel (TMA-staged tiles, QK^T and
+// PV as tcgen05 MMAs into tensor memory, fp32 online softmax with one thread per query row),
+// replacing the reference's fp16 tensor-core path (tensorax csrc/cuda/kernels/attn.cu:1143-1521).
+// What differs is who shares an SM.  With one exponential per score the special-function unit
+// is the busiest pipe of this kernel; two independent CTAs per SM fall into step on it (both
+// in their exponential phase, then both in their hand-over phase) and the unit idles half of
+// the time.  Here ONE CTA owns the SM and works on two 128-row query tiles of the same head:
+//   warp 0        TMA producer: both Q tiles once, then every K / V tile ONCE for both query
+//                 tiles through an NS-deep ring
+//   warp 1        issues every MMA, in a fixed order that alternates between the two tiles
+//   warps 2-3     idle (they only give their registers away)
+//   warps 4-7     softmax of query tile 0 (thread = row = tensor-memory lane)
+//   warps 8-11    softmax of query tile 1
+// and the two softmax warps that share a scheduler pass a token (an mbarrier pair) around
+// their exponential phases, so that they run in anti-phase: while one computes exponentials
+// the other waits for S, pulls it into registers, finds the row max and stores P.
+//
+// Tensor memory (512 columns): S0 | S1 | O0 | O1 | P0 | P1   (P_ALIAS = false), or
+//                              S0/P0 | S1/P1 | O0 | O1        (P_ALIAS = true: P overwrites the
+//                              first half of the S columns it came from; then the next QK^T of
+//                              that tile is issued after its PV, in program order).
+// Every mbarrier wait is bounded; a wait that runs out records a code in `status` and the
+// whole CTA drains and frees its tensor memory.
+#pragma once
+#include "ptx.cuh"
+#include "sdpa_tc.cuh"
+
+namespace txb {
+
+enum PairSection : int {
+    PSEC_SM_TOTAL = 0, PSEC_SM_WAIT_S = 1, PSEC_SM_LOAD_S = 2, PSEC_SM_MAX = 3, PSEC_SM_TOKEN = 4, PSEC_SM_EXP = 5,
+    PSEC_SM_WAIT_PV = 6, PSEC_SM_STORE_P = 7, PSEC_SM_EPILOGUE = 9, PSEC_SM_TILES = 10,
+    PSEC_MMA_TOTAL = 16, PSEC_MMA_WAIT_S = 17, PSEC_MMA_WAIT_K = 18, PSEC_MMA_WAIT_P = 19, PSEC_MMA_WAIT_V = 20,
+    PSEC_MMA_ISSUE = 21,
+};
+
+// POLY: bit e set = element e of every group of 16 exponentials is evaluated on the FMA pipe
+//       (bits come in pairs 2k, 2k+1: the polynomial works on two-wide fp32 vectors).
+// TOKEN: 0 = the two softmax warps of a scheduler run unsynchronised; 1 = they alternate.
+// REL:  the token is handed on after this many of a tile's BN exponentials (BN = at the end).
+template <int D_, int BN_, int NS_, int POLY_, int TOKEN_, int REL_, bool P_ALIAS_, bool PROF_ = false>
+struct PairCfg {
+    static constexpr int D = D_, BN = BN_, NS = NS_, POLY = POLY_, TOKEN = TOKEN_, REL = REL_;
+    static constexpr bool P_ALIAS = P_ALIAS_, PROF = PROF_;
+    static constexpr int BM = 128;
+    static constexpr int THREADS = 384;
+    static constexpr int REGS_LIGHT = 56, REGS_SOFTMAX = 224;   // 128 * 56 + 256 * 224 = 64512 <= 65536
+    static constexpr int KP = D / 64;                      // 64-column panels per row
+    static constexpr uint32_t Q_TILE_BYTES = BM * D * 2;
+    static constexpr uint32_t K_BYTES = BN * D * 2;
+    static constexpr uint32_t V_BYTES = BN * D * 2;
+    static constexpr uint32_t KV_PANEL = BN * 128;
+    static constexpr uint32_t OFF_Q = 0;
+    static constexpr uint32_t OFF_K = 2 * Q_TILE_BYTES;
+    static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_V + NS * V_BYTES;
+    // q_full[2] s_full[2] s_free[2] p_full[2] pv_done[2] tok[2][4] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
+    static constexpr int N_BARS = 18 + 4 * NS;
+    static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
+    static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
+    static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
+    static constexpr uint32_t COL_S0 = 0, COL_S1 = BN;
+    static constexpr uint32_t COL_O0 = 2 * BN, COL_O1 = 2 * BN + D;
+    static constexpr uint32_t COL_P0 = P_ALIAS ? COL_S0 : 2 * BN + 2 * D;
+    static constexpr uint32_t COL_P1 = P_ALIAS ? COL_S1 : 2 * BN + 2 * D + BN / 2;
+    static constexpr uint32_t COLS_USED = P_ALIAS ? 2 * BN + 2 * D : 3 * BN + 2 * D;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static_assert(D % 64 == 0 && BN % 32 == 0 && BN <= 256 && D <= 256, "tile shape");
+    static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
+    static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA may have");
+    static_assert(REL % 4 == 0 && REL > 0 && REL <= BN, "token release point");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const TcParams p)
+{
+    constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const uint32_t q_s = sbase + Cfg::OFF_Q, k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V;
+    const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+    // per-tile barriers: index t = 0, 1
+    const uint32_t q_full = bar0, s_full = bar0 + 16, s_free = bar0 + 32, p_full = bar0 + 48, pv_done = bar0 + 64;
+    const uint32_t tok = bar0 + 80;                     // tok + 8 * (4 * t + quarter): "tile t's warp may compute exponentials"
+    const uint32_t k_full = bar0 + 144, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS, v_empty = v_full + 8 * NS;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    long long prof_last = 0;
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    auto tick = [&](int i) {
+        if constexpr (Cfg::PROF) {
+            if (prof_on) {
+                const long long now = clock64();
+                prof_acc[i] += now - prof_last;
+                prof_last = now;
+            }
+        }
+    };
+    auto tick_start = [&]() {
+        if constexpr (Cfg::PROF) {
+            if (prof_on) prof_last = clock64();
+        }
+    };
+
+    const int q_pair = (int)gridDim.x - 1 - (int)blockIdx.x;     // long (late) causal tiles first
+    const int q0 = q_pair * (2 * BM);                            // first row of tile 0; tile 1 starts at q0 + BM
+    const int bh = blockIdx.y;
+    const int b = bh / p.Hq, h = bh % p.Hq;
+    const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
+
+    int kv_limit = p.Sk;                                         // keys any row of this batch may see
+    if (p.kv_lens) kv_limit = min(kv_limit, max(p.kv_lens[b], 0));
+    // key tiles each query tile walks; tile 1 does not exist when the sequence ends inside tile 0
+    const bool live1 = q0 + BM < p.Sq;
+    const int kv_end0 = p.causal ? min(kv_limit, q0 + BM) : kv_limit;
+    const int kv_end1 = live1 ? (p.causal ? min(kv_limit, q0 + 2 * BM) : kv_limit) : 0;
+    const int n0 = (kv_end0 + BN - 1) / BN, n1 = (kv_end1 + BN - 1) / BN;
+    const int n_max = max(n0, n1), n_alt = min(n0, n1);
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int t = 0; t < 2; ++t) {
+            ptx::mbar_init(q_full + 8 * t, 1);
+            ptx::mbar_init(s_full + 8 * t, 1);
+            ptx::mbar_init(s_free + 8 * t, 4);          // one arrival per softmax warp of the tile
+            ptx::mbar_init(p_full + 8 * t, 4);
+            ptx::mbar_init(pv_done + 8 * t, 1);
+            for (int w = 0; w < 4; ++w) ptx::mbar_init(tok + 8 * (4 * t + w), 1);
+        }
+        for (int s = 0; s < NS; ++s) {
+            ptx::mbar_init(k_full + 8 * s, 1);
+            ptx::mbar_init(k_empty + 8 * s, 1);
+            ptx::mbar_init(v_full + 8 * s, 1);
+            ptx::mbar_init(v_empty + 8 * s, 1);
+        }
+        ptx::fence_mbar_init();
+        if (sbase & 1023u) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_ALIGN); }
+        if (*reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;   // an earlier CTA already gave up
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), Cfg::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const bool run = (*abort_flag == 0) && n_max > 0;
+    // The launch gives every thread 168 registers (65536 / 384); the producer / MMA warpgroup needs
+    // few and hands the rest to the softmax warpgroups, whose score rows then stay in registers.
+
+    if (warp < 4) {
+    ptx::setmaxnreg_dec<Cfg::REGS_LIGHT>();
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (run) {
+            const bool leader = ptx::elect_one();
+            if (leader) {
+                ptx::prefetch_tmap(&tm_q);
+                ptx::prefetch_tmap(&tm_k);
+                ptx::prefetch_tmap(&tm_v);
+                if (n0 > 0) {
+                    ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_TILE_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+                }
+            }
+            __syncwarp();
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                if (leader) {
+                    ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k, k_full + 8 * s,
+                                         pn * 64, j * BN, kvh);
+                    if (j == 0 && n1 > 0) {
+                        ptx::mbar_arrive_expect_tx(q_full + 8, Cfg::Q_TILE_BYTES);
+#pragma unroll
+                        for (int pn = 0; pn < Cfg::KP; ++pn)
+                            ptx::tma_load_3d(q_s + Cfg::Q_TILE_BYTES + pn * (BM * 128), &tm_q, q_full + 8, pn * 64,
+                                             q0 + BM, bh);
+                    }
+                }
+                __syncwarp();
+                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                if (leader) {
+                    ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(v_s + s * Cfg::V_BYTES + pn * Cfg::KV_PANEL, &tm_v, v_full + 8 * s,
+                                         pn * 64, j * BN, kvh);
+                }
+                __syncwarp();
+            }
+            if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_PRODUCER); }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (run) {
+            const bool leader = ptx::elect_one();
+            constexpr uint32_t idesc_qk = ptx::idesc_f16(BM, BN, false);
+            constexpr uint32_t idesc_pv = ptx::idesc_f16(BM, D, true);
+            constexpr uint32_t desc_hi = ptx::smem_desc_sw128_hi(1024);
+            const uint32_t q_lo = ptx::smem_desc_sw128_lo(q_s, 16);
+            const uint32_t k_lo = ptx::smem_desc_sw128_lo(k_s, 16);
+            const uint32_t v_lo = ptx::smem_desc_sw128_lo(v_s, Cfg::KV_PANEL);
+            bool ok = true;
+            // S_t = Q_t K_j^T; the K stage is released by whichever tile reads it last
+            auto issue_qk = [&](int t, int j) -> bool {
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                tick(0);
+                if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag)) return false;
+                tick(2);
+                ptx::tc_fence_after_sync();
+                const uint32_t ks_lo = k_lo + (uint32_t)s * (Cfg::K_BYTES >> 4);
+                const uint32_t qt_lo = q_lo + (uint32_t)t * (Cfg::Q_TILE_BYTES >> 4);
+                const uint32_t t_s = tmem + (t ? Cfg::COL_S1 : Cfg::COL_S0);
+                const bool last_reader = t == 1 ? true : (j >= n1);
+                if (leader) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t qa = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;
+                        const uint32_t kb = ((kk >> 2) * Cfg::KV_PANEL + (kk & 3) * 32) >> 4;
+                        ptx::mma_ss(t_s, ptx::make_desc(qt_lo + qa, desc_hi), ptx::make_desc(ks_lo + kb, desc_hi),
+                                    idesc_qk, kk > 0);
+                    }
+                    if (last_reader) ptx::mma_commit(k_empty + 8 * s);
+                    ptx::mma_commit(s_full + 8 * t);
+                }
+                __syncwarp();
+                tick(5);
+                return true;
+            };
+            // O_t += P_t V_j
+            auto issue_pv = [&](int t, int j) -> bool {
+                const int s = j % NS;
+                const uint32_t ph = (uint32_t)(j / NS) & 1u;
+                tick(0);
+                if (!ptx::mbar_wait(v_full + 8 * s, ph, abort_flag)) return false;
+                tick(4);
+                if (!ptx::mbar_wait(p_full + 8 * t, (uint32_t)j & 1u, abort_flag)) return false;
+                tick(3);
+                ptx::tc_fence_after_sync();
+                const uint32_t vs_lo = v_lo + (uint32_t)s * (Cfg::V_BYTES >> 4);
+                const uint32_t t_o = tmem + (t ? Cfg::COL_O1 : Cfg::COL_O0);
+                const uint32_t t_p = tmem + (t ? Cfg::COL_P1 : Cfg::COL_P0);
+                const bool last_reader = t == 1 ? true : (j >= n1);
+                if (leader) {
+#pragma unroll
+                    for (int kk = 0; kk < BN / 16; ++kk) {
+                        const uint64_t bdesc = ptx::make_desc(vs_lo + kk * ((16 * 128) >> 4), desc_hi);
+                        ptx::mma_ts(t_o, t_p + kk * 8, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    if (last_reader) ptx::mma_commit(v_empty + 8 * s);
+                    ptx::mma_commit(pv_done + 8 * t);
+                }
+                __syncwarp();
+                tick(5);
+                return true;
+            };
+            tick_start();
+            const long long t_begin = Cfg::PROF ? clock64() : 0;
+            if (n0 > 0) {
+                ok = ptx::mbar_wait(q_full, 0, abort_flag);
+                if (ok) ok = issue_qk(0, 0);
+            }
+            if (ok && n1 > 0) {
+                ok = ptx::mbar_wait(q_full + 8, 0, abort_flag);
+                if (ok) ok = issue_qk(1, 0);
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const int nt = t ? n1 : n0;
+                    if constexpr (!Cfg::P_ALIAS) {
+                        if (j + 1 < nt && ok) {
+                            tick(0);
+                            ok = ptx::mbar_wait(s_free + 8 * t, (uint32_t)j & 1u, abort_flag);
+                            tick(1);
+                            if (ok) { ptx::tc_fence_after_sync(); ok = issue_qk(t, j + 1); }
+                        }
+                        if (j < nt && ok) ok = issue_pv(t, j);
+                    } else {
+                        // P_t lives in S_t's columns: the next QK^T of this tile follows its PV in program order
+                        if (j < nt && ok) ok = issue_pv(t, j);
+                        if (j + 1 < nt && ok) ok = issue_qk(t, j + 1);
+                    }
+                }
+            }
+            if (!ok && leader) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_MMA); }
+            if constexpr (Cfg::PROF) {
+                if (prof_on && leader) {
+                    p.prof[PSEC_MMA_TOTAL] = clock64() - t_begin;
+                    p.prof[PSEC_MMA_WAIT_S] = prof_acc[1];
+                    p.prof[PSEC_MMA_WAIT_K] = prof_acc[2];
+                    p.prof[PSEC_MMA_WAIT_P] = prof_acc[3];
+                    p.prof[PSEC_MMA_WAIT_V] = prof_acc[4];
+                    p.prof[PSEC_MMA_ISSUE] = prof_acc[5];
+                }
+            }
+        }
+    }
+    } else {
+        ptx::setmaxnreg_inc<Cfg::REGS_SOFTMAX>();
+        // ------------------------------------------------------------ softmax + epilogue
+        const int t = (warp - 4) >> 2;                   // query tile of this warp
+        const int quarter = warp & 3;                    // tensor-memory lanes this warp may touch
+        const int r = quarter * 32 + lane;               // row inside the tile
+        const int q0t = q0 + t * BM;
+        const int row = q0t + r;
+        const int nt = t ? n1 : n0;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem + lane_base + (t ? Cfg::COL_S1 : Cfg::COL_S0);
+        const uint32_t t_o = tmem + lane_base + (t ? Cfg::COL_O1 : Cfg::COL_O0);
+        const uint32_t t_p = tmem + lane_base + (t ? Cfg::COL_P1 : Cfg::COL_P0);
+        const uint32_t my_s_full = s_full + 8 * t, my_s_free = s_free + 8 * t, my_p_full = p_full + 8 * t,
+                       my_pv_done = pv_done + 8 * t;
+        const uint32_t my_tok = tok + 8 * (4 * t + quarter), other_tok = tok + 8 * (4 * (t ^ 1) + quarter);
+        const float scale = p.scale_log2;
+        float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
+        float l = 0.f;
+        bool ok = run && nt > 0;
+        auto arrive_warp = [&](uint32_t bar) {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar);
+        };
+        // Token protocol per scheduler: tile 0's warp goes first; each hands on after (part of) its
+        // exponentials.  It covers the first n_alt key tiles, which both query tiles walk; the
+        // tile with more key tiles runs the rest alone.
+        if (Cfg::TOKEN && t == 1 && n_alt > 0 && lane == 0) ptx::mbar_arrive(other_tok);
+        const bool prof_lane = prof_on && quarter == 0 && lane == 0;
+        tick_start();
+        const long long t_begin = Cfg::PROF ? clock64() : 0;
+        for (int j = 0; j < nt && ok; ++j) {
+            const int kv0 = j * BN;
+            tick(0);
+            ok = ptx::mbar_wait(my_s_full, (uint32_t)j & 1u, abort_flag);
+            tick(PSEC_SM_WAIT_S);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            uint32_t sv[BN];
+            ptx::tmem_ld_cols<BN>(t_s, sv);
+            ptx::tmem_wait_ld();
+            ptx::reg_fence_cols<BN>(sv);
+            if constexpr (!Cfg::P_ALIAS) arrive_warp(my_s_free);
+            tick(PSEC_SM_LOAD_S);
+
+            const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0t));
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int col = kv0 + i;
+                    const bool vis = col < kv_limit && (!p.causal || col <= row);
+                    if (!vis) sv[i] = 0xff800000u;       // -inf
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN; i += 8) {
+                mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_new = fmaxf(m_used, mx * scale);
+            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+            m_used = m_next;
+            tick(PSEC_SM_MAX);
+            const bool tokened = Cfg::TOKEN && j < n_alt;
+            if (tokened) {
+                ok = ptx::mbar_wait(my_tok, (uint32_t)j & 1u, abort_flag);
+                if (!ok) break;
+            }
+            tick(PSEC_SM_TOKEN);
+            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+            const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
+            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+            uint32_t pk[BN / 2];
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
+                                             scale2, negm2);
+                const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
+                                             scale2, negm2);
+                const int e0 = i & 15;
+                const bool poly_a = (Cfg::POLY >> e0) & 1, poly_b = (Cfg::POLY >> (e0 + 2)) & 1;
+                const float2 ea = poly_a ? ptx::ex2_poly2(xa) : make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                const float2 eb = poly_b ? ptx::ex2_poly2(xb) : make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                sum_a = __fadd2_rn(sum_a, ea);
+                sum_b = __fadd2_rn(sum_b, eb);
+                pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
+                if (Cfg::TOKEN && i + 4 == Cfg::REL && Cfg::REL < BN) {
+                    // hand the token on early: the partner starts while this warp finishes its tail
+                    if (tokened && (t == 0 || j + 1 < n_alt)) {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(other_tok);
+                    }
+                }
+            }
+            l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
+            if (Cfg::TOKEN && Cfg::REL == BN) {
+                if (tokened && (t == 0 || j + 1 < n_alt)) {
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(other_tok);
+                }
+            }
+            tick(PSEC_SM_EXP);
+            if (j > 0) {
+                // PV of the previous tile must be finished before P is overwritten or O rescaled
+                ok = ptx::mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_flag);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D / 16; ++c) {
+                        uint32_t o[16];
+                        ptx::tmem_ld16(t_o + c * 16, o);
+                        ptx::tmem_wait_ld();
+                        ptx::reg_fence16(o);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st16(t_o + c * 16, o);
+                    }
+                    ptx::tmem_wait_st();
+                }
+            }
+            tick(PSEC_SM_WAIT_PV);
+            ptx::tmem_st_cols<BN / 2>(t_p, pk);
+            ptx::tmem_wait_st();
+            arrive_warp(my_p_full);
+            tick(PSEC_SM_STORE_P);
+        }
+        const long long t_loop_end = Cfg::PROF ? clock64() : 0;
+        if (run && nt > 0 && ok) {
+            ok = ptx::mbar_wait(my_pv_done, (uint32_t)(nt - 1) & 1u, abort_flag);
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
+                const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total;
+                float *orow = static_cast<float *>(p.out) + obase;
+                __half *orow_h = static_cast<__half *>(p.out) + obase;
+                if (p.lse && row < p.Sq) p.lse[(size_t)bh * p.Sq + row] = m_used + __log2f(l);
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld32(t_o + c * 32, o);
+                    ptx::tmem_wait_ld();
+                    ptx::reg_fence32(o);
+                    if (row < p.Sq) {
+                        if (p.out_f16) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 hh;
+                                hh.x = ptx::pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                                hh.y = ptx::pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                                hh.z = ptx::pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                                hh.w = ptx::pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                                *reinterpret_cast<uint4 *>(orow_h + c * 32 + i) = hh;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 f;
+                                f.x = __uint_as_float(o[i]) * inv_l;
+                                f.y = __uint_as_float(o[i + 1]) * inv_l;
+                                f.z = __uint_as_float(o[i + 2]) * inv_l;
+                                f.w = __uint_as_float(o[i + 3]) * inv_l;
+                                *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (run && nt > 0 && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
+        if constexpr (Cfg::PROF) {
+            if (prof_lane) {
+                long long *dst = p.prof + (t ? 32 : 0);
+                dst[PSEC_SM_TOTAL] = t_loop_end - t_begin;
+                for (int i = 1; i <= 7; ++i) dst[i] = prof_acc[i];
+                dst[PSEC_SM_EPILOGUE] = clock64() - t_loop_end;
+                dst[PSEC_SM_TILES] = nt;
+            }
+        }
+        if (nt == 0 && *abort_flag == 0 && row < p.Sq && (t == 0 || live1)) {
+            // no visible key at all for this tile: the reference's 0/0
+            const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total;
+            if (p.out_f16) {
+                __half *orow_h = static_cast<__half *>(p.out) + obase;
+                for (int i = 0; i < D; ++i) orow_h[i] = __ushort_as_half((unsigned short)0x7e00);
+            } else {
+                float *orow = static_cast<float *>(p.out) + obase;
+                for (int i = 0; i < D; ++i) orow[i] = __int_as_float(0x7fc00000);
+            }
+            if (p.lse) p.lse[(size_t)bh * p.Sq + row] = __int_as_float(0x7fc00000);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);   // let copies in flight land
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace txb

@@ -72,6 +72,9 @@ def shard_arrays(shard: Shard, q, k, v, kv_lens: Optional[Sequence[int]] = None)
 def place_output(shard: Shard, full_out, local_out) -> None:
     """Write a rank's [n, group, Sq, d_v] result into the full [B, Hq, Sq, d_v] array."""
     B, Hq, Sq, dv = full_out.shape
+    if not full_out.flags.c_contiguous:
+        raise ValueError("place_output: the full array must be C-contiguous (a reshape of anything else is a copy, "
+                         "and the rank's result would be written into that copy)")
     flat = full_out.reshape(B * Hq, Sq, dv)
     flat[shard.q_head_begin:shard.q_head_end] = local_out.reshape(-1, Sq, dv)
 
@@ -86,4 +89,6 @@ def shard_grad(shard: Shard, grad):
 def place_kv_grad(shard: Shard, full_grad, local_grad) -> None:
     """Write a rank's [n, 1, Sk, d] dK or dV into the full [B, Hkv, Sk, d] array."""
     B, Hkv, Sk, d = full_grad.shape
+    if not full_grad.flags.c_contiguous:
+        raise ValueError("place_kv_grad: the full array must be C-contiguous")
     full_grad.reshape(B * Hkv, Sk, d)[shard.unit_begin:shard.unit_end] = local_grad.reshape(-1, Sk, d)

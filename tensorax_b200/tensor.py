@@ -148,6 +148,16 @@ class Tensor:
         g = grad if grad.dtype == "float32" else None
         if g is None or g.device != "cuda":
             raise RuntimeError("SDPA backward: grad must be a float32 CUDA tensor")
+        # Checked before any kernel runs or any .grad is touched: the same tensor passed twice (q is k, k is v)
+        # would need its two gradients added, and an input that already holds a gradient would need accumulation.
+        wanted = [t for t in (query, key, value) if t.requires_grad]
+        if len({id(t) for t in wanted}) != len(wanted):
+            self.grad = None
+            raise RuntimeError("SDPA backward: the same tensor was passed as more than one of query/key/value; "
+                               "summing its gradients is outside tensorax_b200 -- pass copies")
+        if any(t.grad is not None for t in wanted):
+            self.grad = None
+            raise RuntimeError("gradient accumulation is not available in tensorax_b200: clear .grad of the inputs first")
         dq, dk, dv = _C.scaled_dot_product_attention_backward(
             query._c_tensor, key._c_tensor, value._c_tensor, self._c_tensor, saved["lse"], g._c_tensor,
             causal=saved["causal"], kv_lens=saved["kv_lens"])

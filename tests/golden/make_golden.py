@@ -1,8 +1,8 @@
 """Generates tests/golden/sdpa_golden.npz by running the REFERENCE's own CPU SDPA.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has the reference checkout (TENSORAX_REF=<path to it>):
 
-    make -C oracle ref && python tests/golden/make_golden.py
+    make -C oracle ref REF=$TENSORAX_REF && python tests/golden/make_golden.py
 
 It calls ``tensorax::sdpa_cpu`` (csrc/cpu/tensor_cpu.cpp:464-529) through
 oracle/_ref/libtensorax_ref_cpu.so -- the reference's source compiled where it

@@ -102,3 +102,15 @@ def test_two_gloo_ranks_reassemble_the_full_result(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert "SHARD_OK" in proc.stdout
+
+
+def test_placing_into_a_non_contiguous_array_is_refused():
+    """A transposed view reshapes into a copy: the rank's result would vanish, so the helpers raise."""
+    sh = sharding.partition(2, 2, 4, 2, 0)
+    full = np.zeros((8, 4, 2, 4), dtype=np.float32).transpose(1, 2, 0, 3)      # [4, 2, 8, 4], not C-contiguous
+    assert full.shape == (4, 2, 8, 4) and not full.flags.c_contiguous
+    with pytest.raises(ValueError):
+        sharding.place_output(sh, np.zeros((2, 4, 8, 4), np.float32).transpose(0, 1, 3, 2).transpose(0, 1, 3, 2)[:, :, ::-1],
+                              np.zeros((sh.n_units, sh.group, 8, 4), np.float32))
+    with pytest.raises(ValueError):
+        sharding.place_kv_grad(sh, full[:2], np.zeros((sh.n_units, 1, 8, 4), np.float32))
