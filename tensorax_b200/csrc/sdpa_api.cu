@@ -285,23 +285,22 @@ int launch_variant(int variant, const tx_sdpa_desc *d, cudaStream_t st, int *sta
     case 10: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0003>>(d, st, status, prof);
     case 11: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0303>>(d, st, status, prof);
     case 12: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0333>>(d, st, status, prof);
-    // d = 64, one CTA per SM, two query tiles
-    case 1: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 0, 128, false, PROF>>(d, st, status, prof);
-    case 2: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 1, 128, false, PROF>>(d, st, status, prof);
-    case 3: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, 1, 96, false, PROF>>(d, st, status, prof);
-    case 4: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 128, false, PROF>>(d, st, status, prof);
-    case 5: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 96, false, PROF>>(d, st, status, prof);
-    case 6: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, 1, 128, false, PROF>>(d, st, status, prof);
-    case 7: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 1, 64, false, PROF>>(d, st, status, prof);
-    case 8: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, 0, 128, false, PROF>>(d, st, status, prof);
-    case 9: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, 1, 96, false, PROF>>(d, st, status, prof);
+    // d = 64, one CTA per SM, two query tiles: PairCfg<D, BN, NS, POLY, SPEC, PREFETCH, LAYOUT, PROF, CHUNK_ST>
+    case 1: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
+    case 2: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, false, false, 0, PROF>>(d, st, status, prof);
+    case 3: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, false, false, 0, PROF>>(d, st, status, prof);
+    case 4: return launch_pair_t<PairCfg<64, 128, 4, 0x3333, false, false, 0, PROF>>(d, st, status, prof);
+    case 5: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, true, false, 0, PROF>>(d, st, status, prof);
+    case 6: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, false, false, 0, PROF, true>>(d, st, status, prof);
+    case 7: return launch_pair_t<PairCfg<64, 128, 3, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
+    case 8: return launch_pair_t<PairCfg<64, 128, 5, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
+    case 9: return launch_pair_t<PairCfg<64, 128, 4, 0, false, false, 0, PROF>>(d, st, status, prof);
     // d = 128
     case 20: return launch_tc_t<TcCfg<128, 128, 64, 2, true, PROF>>(d, st, status, prof);
-    case 21: return launch_pair_t<PairCfg<128, 128, 2, 0, 1, 128, true, PROF>>(d, st, status, prof);
-    case 22: return launch_pair_t<PairCfg<128, 128, 2, 0, 0, 128, true, PROF>>(d, st, status, prof);
-    case 23: return launch_pair_t<PairCfg<128, 64, 4, 0, 1, 64, false, PROF>>(d, st, status, prof);
-    case 24: return launch_pair_t<PairCfg<128, 128, 2, 0x0003, 1, 128, true, PROF>>(d, st, status, prof);
-    case 25: return launch_pair_t<PairCfg<128, 128, 2, 0x0003, 1, 96, true, PROF>>(d, st, status, prof);
+    case 21: return launch_pair_t<PairCfg<128, 64, 4, 0, false, false, 2, PROF>>(d, st, status, prof);
+    case 22: return launch_pair_t<PairCfg<128, 64, 4, 0, true, true, 2, PROF>>(d, st, status, prof);
+    case 23: return launch_pair_t<PairCfg<128, 128, 2, 0, false, false, 1, PROF>>(d, st, status, prof);
+    case 24: return launch_pair_t<PairCfg<128, 64, 4, 0x0003, true, true, 2, PROF>>(d, st, status, prof);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: unknown kernel variant %d", variant);
 }
@@ -316,12 +315,12 @@ int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
     case 64: {
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
         const int v = variant_env("TX_SDPA_D64_VARIANT");
-        return launch_variant<false>(v >= 0 && v < 20 ? v : 0, d, st, status, nullptr);
+        return launch_variant<false>(v >= 0 && v < 20 ? v : 1, d, st, status, nullptr);
     }
     case 128: {
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
         const int v = variant_env("TX_SDPA_D128_VARIANT");
-        return launch_variant<false>(v >= 20 ? v : 20, d, st, status, nullptr);
+        return launch_variant<false>(v >= 20 ? v : 23, d, st, status, nullptr);
     }
     case 256:
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
@@ -944,10 +943,10 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     if (rc == TX_OK) {
         if (d->d_k == 64) {
             const int v = variant_env("TX_SDPA_D64_VARIANT");
-            rc = launch_variant<true>(v >= 0 && v < 20 ? v : 0, d, st, status, dev);
+            rc = launch_variant<true>(v >= 0 && v < 20 ? v : 1, d, st, status, dev);
         } else if (d->d_k == 128) {
             const int v = variant_env("TX_SDPA_D128_VARIANT");
-            rc = launch_variant<true>(v >= 20 ? v : 20, d, st, status, dev);
+            rc = launch_variant<true>(v >= 20 ? v : 23, d, st, status, dev);
         }
         else if (d->d_k == 256) rc = launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, dev);
         else rc = launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, true, 0, 1, true, 160, true>>(d, st, status, dev);
