@@ -196,16 +196,31 @@ TX_API int tx_sdpa_optimized_flash_profile_sections_cuda(const float *Q, const f
                                                          int64_t num_heads, int64_t seq_len_q, int64_t seq_len_k,
                                                          int64_t d_k, int64_t d_v, long long *ticks32);
 
-/* ---- section profile: reference csrc/tensor_ops.cpp:1434-1507 (profile_sections_sdpa_*) over the
- *      TX_TICK clock64 sections of csrc/cuda/profiling.cuh:20-51.  Runs `desc` once on an instrumented
- *      build of the tensor-core kernel (d = 64 or 128) and returns 32 cycle counters of CTA (0,0,0),
- *      summed over its key tiles.  Softmax lane: [0] loop total, [1] wait for S, [2] S -> registers,
- *      [3] mask + row max, [5] exponentials + pack + sum,
- *      [6] wait for the previous PV, [7] O rescale, [8] P store + hand-over, [9] epilogue, [10] tiles.
- *      MMA lane: [16] loop total, [17] wait for S to be consumed, [18] K wait + QK^T issue,
- *      [19] wait for V, [20] wait for P, [21] PV issue.  Producer lane: [24] total, [25] wait for a
- *      free K stage, [26] wait for a free V stage. */
-TX_API int tx_profile_sections_sdpa(const tx_sdpa_desc *desc, long long *ticks32);
+/* ---- section profile of the tensor-core kernels: the counterpart, for the fp16 path, of the reference's
+ *      profile_sections_sdpa_* (csrc/tensor_ops.cpp:1434-1507) over the TX_TICK clock64 sections of
+ *      csrc/cuda/profiling.cuh:20-51.  Runs `desc` (fp16, d in {64,128,256,512}) once on an instrumented build of
+ *      the kernel that serves that shape and returns 64 cycle counters of CTA (0,0,0), summed over its key tiles.
+ *      d = 64, 128 (two query tiles per CTA): softmax lane of query tile 0 in [0..10], of query tile 1 in [32..42]:
+ *        [+0] loop total, [+1] wait for S, [+2] S -> registers, [+3] mask, [+5] row max + exponentials + pack + sum,
+ *        [+6] wait for the previous PV (+ O rescale), [+7] P store + hand-over, [+9] epilogue, [+10] key tiles;
+ *        MMA lane: [16] loop total, [17] wait for S to be consumed, [18] wait for K, [19] wait for P,
+ *        [20] wait for V, [21] MMA issue (blocks while the tensor pipe's queue is full).
+ *      d = 256, 512 (one query tile per CTA): softmax lane [0] loop total, [1] wait for S, [2] S -> registers,
+ *        [3] mask + row max, [5] exponentials + pack + sum, [6] wait for the previous PV, [7] O rescale,
+ *        [8] P store + hand-over, [9] epilogue, [10] key tiles; MMA lane [16] total, [17] wait for S to be consumed,
+ *        [18] K wait + QK^T issue, [19] wait for V, [20] wait for P, [21] PV issue; producer lane [24] total,
+ *        [25] wait for a free K stage, [26] wait for a free V stage.  Entries not listed stay 0. */
+TX_API int tx_profile_sections_sdpa(const tx_sdpa_desc *desc, long long *ticks64);
+
+/* ---- failure-path self-test (no reference counterpart: the reference's device code cannot fail softly, its host
+ *      code prints and exits, csrc/cuda/cuda_utils.cuh:6-14).  Runs `desc` (fp16, d = 64) on an instantiation of the
+ *      production kernel whose bounded waits give up after 2 ms instead of 2 s and whose TMA producer leaves out K
+ *      tile `skip_k_tile` of every CTA (-1: none, the call is then an ordinary forward pass).  With a tile left out
+ *      the MMA warp's wait for it runs out: the CTA records stage code 3 in the device status word, overwrites its
+ *      output rows with NaN, drains, frees its tensor memory and returns; the call waits for the stream and returns
+ *      TX_ERR_KERNEL, as tx_sdpa_finish does after any kernel that gave up.  Nothing faults, traps or spins without
+ *      bound, and the context stays usable: the next ordinary launch is unaffected. */
+TX_API int tx_selftest_wait_timeout(const tx_sdpa_desc *desc, int32_t skip_k_tile);
 
 /* ---- backward: the reference's autograd rule for 'scaled_dot_product_attention'
  *      (tensorax/tensor.py:806-827: dV = P^T dO, dP = dO V^T, dS = P o (dP - rowsum(dP o P)) / sqrt(d),

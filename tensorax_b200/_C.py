@@ -344,10 +344,10 @@ def scaled_dot_product_attention_mma_fp16(query, key, value) -> TensorImpl:
 
 
 def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
-    """Counterpart of the reference's ``profile_sections_sdpa_*`` bindings
-    (csrc/tensor_ops.cpp:1434-1507, 1622-1636): runs the call once on the instrumented
-    tensor-core kernel (fp16, d = 64 or 128) and returns 32 cycle counters of one CTA; the
-    meaning of each slot is listed beside ``tx_profile_sections_sdpa`` in the C header."""
+    """Section profile of the fp16 tensor-core kernels, the counterpart for that path of the reference's
+    ``profile_sections_sdpa_*`` bindings (csrc/tensor_ops.cpp:1434-1507, 1622-1636): runs the call once on the
+    instrumented kernel of its shape (fp16, d in {64, 128, 256, 512}) and returns 64 cycle counters of one CTA;
+    the meaning of each slot is listed beside ``tx_profile_sections_sdpa`` in the C header."""
     B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, None, "profile_sections")
     if query.device != "cuda" or query.dtype != "float16":
         raise RuntimeError("profile_sections: float16 CUDA tensors expected")
@@ -355,9 +355,45 @@ def profile_sections_sdpa(query, key, value, causal=False) -> List[int]:
     desc = _lib.SdpaDesc(q=query.data_ptr, k=key.data_ptr, v=value.data_ptr, mask=None, kv_lens=None,
                          out=out.data_ptr, batch=B, q_heads=H, kv_heads=Hkv, seq_q=Sq, seq_k=Sk, d_k=dk,
                          d_v=dv, dtype=_lib.TX_DTYPE_F16, causal=int(bool(causal)), flags=0, stream=None)
-    ticks = (ctypes.c_longlong * 32)()
+    ticks = (ctypes.c_longlong * 64)()
     _lib.check(_lib.load().tx_profile_sections_sdpa(ctypes.byref(desc), ticks))
     return list(ticks)
+
+
+def _profile_sections_f32(name, query, key, value, mask=None) -> List[int]:
+    """The reference's ``profile_sections_sdpa_{naive,tiled,flash,mma,flash_optimized}`` (csrc/tensor_ops.cpp:1434-1507):
+    float32 CUDA tensors, 32 clock64 stamps of one instrumented launch of the exact-fp32 kernel."""
+    B, H, Hkv, Sq, Sk, dk, dv = _validate(query, key, value, mask, "profile_sections")
+    if query.device != "cuda":
+        raise RuntimeError("profile_sections requires CUDA tensors")
+    if query.dtype != "float32" or Hkv != H:
+        raise RuntimeError("profile_sections: float32 tensors with equal head counts expected")
+    out = TensorImpl([B, H, Sq, dv], "float32", "cuda")
+    ticks = (ctypes.c_longlong * 32)()
+    fn = getattr(_lib.load(), f"tx_sdpa_{name}_profile_sections_cuda")
+    _lib.check(fn(query.data_ptr, key.data_ptr, value.data_ptr, mask.data_ptr if mask is not None else None,
+                  out.data_ptr, B, H, Sq, Sk, dk, dv, ticks))
+    return list(ticks)
+
+
+def profile_sections_sdpa_naive(q, k, v, mask=None) -> List[int]:
+    return _profile_sections_f32("naive", q, k, v, mask)
+
+
+def profile_sections_sdpa_tiled(q, k, v, mask=None) -> List[int]:
+    return _profile_sections_f32("tiled", q, k, v, mask)
+
+
+def profile_sections_sdpa_flash(q, k, v, mask=None) -> List[int]:
+    return _profile_sections_f32("flash", q, k, v, mask)
+
+
+def profile_sections_sdpa_mma(q, k, v, mask=None) -> List[int]:
+    return _profile_sections_f32("mma", q, k, v, mask)
+
+
+def profile_sections_sdpa_flash_optimized(q, k, v, mask=None) -> List[int]:
+    return _profile_sections_f32("optimized_flash", q, k, v, mask)
 
 
 def scaled_dot_product_attention_ex(query, key, value, mask=None, causal=False, kv_lens=None,

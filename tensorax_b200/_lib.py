@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_backward",
     "tx_sdpa_naive_profile_sections_cuda", "tx_sdpa_tiled_profile_sections_cuda", "tx_sdpa_flash_profile_sections_cuda",
     "tx_sdpa_mma_profile_sections_cuda", "tx_sdpa_optimized_flash_profile_sections_cuda",
+    "tx_selftest_wait_timeout",
 )
 
 
@@ -105,6 +106,7 @@ def load():
     lib.tx_linear_set_cuda_cores_only.argtypes = [c_int]
     lib.tx_sdpa_forward.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
+    lib.tx_selftest_wait_timeout.argtypes = [ctypes.POINTER(SdpaDesc), c_int32]
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_backward.argtypes = [ctypes.POINTER(SdpaBwdDesc)]
     lib.tx_sdpa_uses_tensor_cores.argtypes = [ctypes.POINTER(SdpaDesc)]

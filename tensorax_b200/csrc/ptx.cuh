@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 #include <cstdint>
 
+#include "bounded_wait.h"
+
 namespace txb {
 namespace ptx {
 
@@ -77,30 +79,19 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  `abort_flag` is a shared-memory word any thread of the CTA sets
-// when it gives up; everybody else then stops waiting at once.  The bound is
-// wall-clock (the nanosecond global timer), not a spin count, because one
-// try_wait may itself suspend for a hardware-chosen time.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
+// Bounded wait (the rule itself: bounded_wait.h).  `abort_flag` is a shared-memory word any thread of
+// the CTA sets when it gives up; everybody else then stops waiting at once.
 __device__ __forceinline__ uint64_t global_timer_ns()
 {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs)
 {
-    if (mbar_test_wait(bar, parity)) return true;      // the common case: the phase is already over
-    uint64_t t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 127u) == 127u) {
-            if (*abort_flag) return false;
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
-        }
-    }
+    return bounded_wait([&] { return mbar_test_wait(bar, parity); }, [&] { return mbar_try_wait(bar, parity); },
+                        [] { return global_timer_ns(); }, abort_flag, limit_ns);
 }
 
 // ---------------------------------------------------------------- fences

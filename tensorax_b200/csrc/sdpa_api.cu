@@ -204,8 +204,9 @@ int launch_simt(const txb::SimtParams &p, cudaStream_t st)
 }
 
 // Elements (bit e = element e of each group of 16) whose exponential is evaluated by the FMA-pipe
-// polynomial at d = 64; measured round-robin against 0, 1, 3 and 4 of 16 and other placements.
-constexpr int kPolyMaskD64 = 0x0202;
+// polynomial at d = 64: two whole pairs of 16 (the polynomial is evaluated two-wide); measured round-robin
+// against 0, 1, 3 and 4 pairs of 8.
+constexpr int kPolyPairsD64 = 0x0303;
 
 template <class Cfg>
 int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
@@ -228,6 +229,7 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     p.causal = d->causal ? 1 : 0;
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
     p.prof = prof;
+    p.skip_k_tile = -1;
     TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::SMEM_BYTES));
     dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads),
@@ -239,7 +241,7 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
 }
 
 template <class Cfg>
-int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
+int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr, int skip_k_tile = -1)
 {
     CUtensorMap tq, tk, tv;
     if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, d->d_k, Cfg::BM)) return rc;
@@ -259,6 +261,7 @@ int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long
     p.causal = d->causal ? 1 : 0;
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
     p.prof = prof;
+    p.skip_k_tile = skip_k_tile;
     TX_CUDA(cudaFuncSetAttribute(txb::sdpa_tc_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Cfg::SMEM_BYTES));
     dim3 grid((unsigned)((d->seq_q + 2 * Cfg::BM - 1) / (2 * Cfg::BM)), (unsigned)(d->batch * d->q_heads), 1);
@@ -268,69 +271,39 @@ int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long
     return TX_OK;
 }
 
-// Experiment switch (kernel variant by number) while the d = 64 / 128 shapes are being tuned.
-int variant_env(const char *name)
-{
-    const char *e = std::getenv(name);
-    return e ? std::atoi(e) : -1;
-}
+// Kernel and tile shape per head dim.
+//   d = 64, 128   sdpa_tc_pair_kernel: one CTA per SM, two 128-row query tiles, 128 keys per tile
+//                 (d = 64: four-deep K/V ring, P in its own tensor-memory columns, a quarter of the
+//                 exponentials on the FMA pipe; d = 128: two-deep ring, P over S)
+//   d = 256       sdpa_tc_kernel, 64 keys per tile, one CTA per SM, Q in tensor memory
+//   d = 512       sdpa_tc_kernel, 64 keys per tile, two CTAs split the value columns
+// `prof` (section profile) selects the instrumented instantiation of the same shape.
+using PairD64 = txb::PairCfg<64, 128, 4, kPolyPairsD64, false>;
+using PairD64Prof = txb::PairCfg<64, 128, 4, kPolyPairsD64, false, true>;
+using PairD128 = txb::PairCfg<128, 128, 2, 0, true>;
+using PairD128Prof = txb::PairCfg<128, 128, 2, 0, true, true>;
 
-template <bool PROF>
-int launch_variant(int variant, const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof)
-{
-    using namespace txb;
-    switch (variant) {
-    // d = 64, two CTAs per SM, one query tile each
-    case 0: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, kPolyMaskD64>>(d, st, status, prof);
-    case 10: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0003>>(d, st, status, prof);
-    case 11: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0303>>(d, st, status, prof);
-    case 12: return launch_tc_t<TcCfg<64, 64, 128, 3, true, PROF, 0x0333>>(d, st, status, prof);
-    // d = 64, one CTA per SM, two query tiles: PairCfg<D, BN, NS, POLY, SPEC, PREFETCH, LAYOUT, PROF, CHUNK_ST>
-    case 1: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
-    case 2: return launch_pair_t<PairCfg<64, 128, 4, 0x0003, false, false, 0, PROF>>(d, st, status, prof);
-    case 3: return launch_pair_t<PairCfg<64, 128, 4, 0x0333, false, false, 0, PROF>>(d, st, status, prof);
-    case 4: return launch_pair_t<PairCfg<64, 128, 4, 0x3333, false, false, 0, PROF>>(d, st, status, prof);
-    case 5: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, true, false, 0, PROF>>(d, st, status, prof);
-    case 6: return launch_pair_t<PairCfg<64, 128, 4, 0x0303, false, false, 0, PROF, true>>(d, st, status, prof);
-    case 7: return launch_pair_t<PairCfg<64, 128, 3, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
-    case 8: return launch_pair_t<PairCfg<64, 128, 5, 0x0303, false, false, 0, PROF>>(d, st, status, prof);
-    case 9: return launch_pair_t<PairCfg<64, 128, 4, 0, false, false, 0, PROF>>(d, st, status, prof);
-    // d = 128
-    case 20: return launch_tc_t<TcCfg<128, 128, 64, 2, true, PROF>>(d, st, status, prof);
-    case 21: return launch_pair_t<PairCfg<128, 64, 4, 0, false, false, 2, PROF>>(d, st, status, prof);
-    case 22: return launch_pair_t<PairCfg<128, 64, 4, 0, true, true, 2, PROF>>(d, st, status, prof);
-    case 23: return launch_pair_t<PairCfg<128, 128, 2, 0, false, false, 1, PROF>>(d, st, status, prof);
-    case 24: return launch_pair_t<PairCfg<128, 64, 4, 0x0003, true, true, 2, PROF>>(d, st, status, prof);
-    }
-    return fail(TX_ERR_UNSUPPORTED, "SDPA: unknown kernel variant %d", variant);
-}
-
-// Tile shapes per head dim (template arguments: DK, DV per CTA, keys per tile, ring depth, P in TMEM).
-//   d= 64: 128 keys/tile, two CTAs per SM      d=128: 64 keys/tile, two CTAs per SM
-//   d=256: 64 keys/tile, one CTA per SM        d=512: 64 keys/tile, two CTAs split the value columns
-int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
 {
     const bool p_smem = (d->flags & TX_SDPA_P_IN_SMEM) != 0;
     switch (d->d_k) {
-    case 64: {
+    case 64:
         if (p_smem) return launch_tc_t<txb::TcCfg<64, 64, 128, 2, false>>(d, st, status);
-        const int v = variant_env("TX_SDPA_D64_VARIANT");
-        return launch_variant<false>(v >= 0 && v < 20 ? v : 1, d, st, status, nullptr);
-    }
-    case 128: {
+        return prof ? launch_pair_t<PairD64Prof>(d, st, status, prof) : launch_pair_t<PairD64>(d, st, status);
+    case 128:
         if (p_smem) return launch_tc_t<txb::TcCfg<128, 128, 64, 2, false>>(d, st, status);
-        const int v = variant_env("TX_SDPA_D128_VARIANT");
-        return launch_variant<false>(v >= 20 ? v : 23, d, st, status, nullptr);
-    }
+        return prof ? launch_pair_t<PairD128Prof>(d, st, status, prof) : launch_pair_t<PairD128>(d, st, status);
     case 256:
         if (p_smem) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, false>>(d, st, status);
         // Narrow key tiles make the A (Q) read the busiest user of the shared-memory port: Q lives
         // in tensor memory instead, and K / V are fetched as two independent queues.
+        if (prof) return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, prof);
         return launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, false, 0, 2, true, 128>>(d, st, status);
     case 512:
         // All 512 tensor-memory columns: S 64 | O 256 | P 32 | first 320 elements of Q 160.  Those five Q panels
         // are staged in the empty K/V ring, so shared memory holds only Q's last three panels (48 KB) beside
         // two 64-key K stages (128 KB) and one V stage (32 KB): 64-key tiles where 32 fitted before.
+        if (prof) return launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, true, 0, 1, true, 160, true>>(d, st, status, prof);
         return launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, false, 0, 1, true, 160, true>>(d, st, status);
     }
     return fail(TX_ERR_UNSUPPORTED, "SDPA: no tensor-core tile shape for d = %lld", (long long)d->d_k);
@@ -926,12 +899,15 @@ int tx_sdpa_forward(const tx_sdpa_desc *desc)
     return forward(desc);
 }
 
-int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
+int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks64)
 {
-    if (!ticks32) return fail(TX_ERR_INVALID, "profile_sections: null output");
+    TX_NVTX_RANGE("sdpa.mma.fp16.profile");
+    if (!ticks64) return fail(TX_ERR_INVALID, "profile_sections: null output");
     if (int rc = validate(d)) return rc;
     if (!tc_eligible(d))
         return fail(TX_ERR_UNSUPPORTED, "profile_sections: built for the tensor-core kernel only");
+    if (d->flags & TX_SDPA_P_IN_SMEM)
+        return fail(TX_ERR_UNSUPPORTED, "profile_sections: not built for the P-in-shared-memory variant");
     if (int rc = ensure_device()) return rc;
     int *status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -940,23 +916,26 @@ int tx_profile_sections_sdpa(const tx_sdpa_desc *d, long long *ticks32)
     cudaStream_t st = static_cast<cudaStream_t>(d->stream);
     int rc = TX_OK;
     if (cudaMemsetAsync(dev, 0, 64 * sizeof(long long), st) != cudaSuccess) rc = fail(TX_ERR_CUDA, "cudaMemsetAsync failed");
-    if (rc == TX_OK) {
-        if (d->d_k == 64) {
-            const int v = variant_env("TX_SDPA_D64_VARIANT");
-            rc = launch_variant<true>(v >= 0 && v < 20 ? v : 1, d, st, status, dev);
-        } else if (d->d_k == 128) {
-            const int v = variant_env("TX_SDPA_D128_VARIANT");
-            rc = launch_variant<true>(v >= 20 ? v : 23, d, st, status, dev);
-        }
-        else if (d->d_k == 256) rc = launch_tc_t<txb::TcCfg<256, 256, 64, 2, true, true, 0, 2, true, 128>>(d, st, status, dev);
-        else rc = launch_tc_t<txb::TcCfg<512, 256, 64, 2, true, true, 0, 1, true, 160, true>>(d, st, status, dev);
-    }
+    if (rc == TX_OK) rc = launch_tc(d, st, status, dev);
     if (rc == TX_OK) rc = finish(st);
-    const size_t n_ticks = std::getenv("TX_SDPA_PROF64") ? 64 : 32;
-    if (rc == TX_OK && cudaMemcpy(ticks32, dev, n_ticks * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+    if (rc == TX_OK && cudaMemcpy(ticks64, dev, 64 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess)
         rc = fail(TX_ERR_CUDA, "cudaMemcpy of the section profile failed");
     (void)cudaFree(dev);
     return rc;
+}
+
+int tx_selftest_wait_timeout(const tx_sdpa_desc *d, int32_t skip_k_tile)
+{
+    if (int rc = validate(d)) return rc;
+    if (!tc_eligible(d) || d->d_k != 64 || (d->flags & TX_SDPA_P_IN_SMEM))
+        return fail(TX_ERR_UNSUPPORTED, "wait-timeout self-test: built for the fp16 d = 64 tensor-core kernel");
+    if (int rc = ensure_device()) return rc;
+    int *status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(d->stream);
+    if (int rc = launch_pair_t<txb::PairCfg<64, 128, 4, kPolyPairsD64, false, false, true>>(d, st, status, nullptr, skip_k_tile))
+        return rc;
+    return finish(st);
 }
 
 int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)

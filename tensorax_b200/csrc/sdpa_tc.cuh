@@ -50,7 +50,8 @@ struct TcParams {
     int causal;
     int out_f16;
     float scale_log2;         // (1/sqrt(d_k)) * log2(e)
-    long long *prof;          // optional [32] cycle counters written by CTA (0,0,0) (section profile)
+    long long *prof;          // optional [64] cycle counters written by CTA (0,0,0) (section profile)
+    int skip_k_tile;          // failure-path self-test instantiation only: the producer leaves this K tile out (-1 = none)
 };
 
 // Section profile (the counterpart of the reference's TX_TICK clock64 sections,
@@ -294,7 +295,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         if (*abort_flag) ok = false;
                         const uint64_t now = ptx::global_timer_ns();
                         if (t_idle == 0) t_idle = now;
-                        else if (now - t_idle > ptx::kWaitLimitNs) ok = false;
+                        else if (now - t_idle > kWaitLimitNs) ok = false;
                     }
                 }
             } else {
@@ -659,6 +660,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag) {
+        // A wait ran out somewhere in this CTA (or in an earlier one of the launch): its rows are not valid.
+        // They are overwritten with NaN so that the failure is visible in the data, not only in the status word.
+        if (warp >= 2) {
+            const int row_a = q0 + (warp & 3) * 32 + lane;
+            if (row_a < p.Sq) {
+                const size_t ob = ((size_t)bh * p.Sq + row_a) * p.dv_total + dv0;
+                for (int i = 0; i < DV; ++i) {
+                    if (p.out_f16) static_cast<__half *>(p.out)[ob + i] = __ushort_as_half((unsigned short)0x7e00);
+                    else static_cast<float *>(p.out)[ob + i] = __int_as_float(0x7fc00000);
+                }
+            }
+        }
         // give copies that may still be in flight time to land before the CTA's memory goes away
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
         __syncthreads();

@@ -5,35 +5,23 @@
 // replacing the reference's fp16 tensor-core path (tensorax csrc/cuda/kernels/attn.cu:1143-1521).
 // ONE CTA owns the SM and works on two 128-row query tiles of the same head:
 //   warp 0        TMA producer: both Q tiles once, then every K / V tile ONCE for both query
-//                 tiles through an NS-deep ring
-//   warp 1        issues every MMA in a fixed order that alternates between the two tiles and
-//                 parks on the barrier of the next one
+//                 tiles through an NS-deep ring (half the L2 -> shared-memory traffic of one
+//                 CTA per query tile)
+//   warp 1        issues every MMA in the fixed order QK0, PV0, QK1, PV1 and parks on the
+//                 barrier of the next one
 //   warps 2-3     idle (they only give their registers away)
 //   warps 4-7     softmax of query tile 0 (thread = row = tensor-memory lane)
 //   warps 8-11    softmax of query tile 1
 // The producer / MMA warpgroup keeps 56 registers per thread and the softmax warpgroups take
-// 224 (setmaxnreg).
+// 224 (setmaxnreg), so a 128-wide score row, its packed P and the exponent pipeline stay in
+// registers without spills.
 //
-// Tensor memory (512 columns), by LAYOUT:
-//   0   S0 | S1 | O0 | O1 | P0 | P1      QK^T of the next key tile is issued once the softmax
-//                                         warps have pulled S into registers
-//   1   S0/P0 | S1/P1 | O0 | O1           P overwrites the first half of the S columns it came
-//                                         from; the next QK^T of that tile follows its PV in
-//                                         program order
-//   2   S0a/P | S0b/P | S1a/P | S1b/P | O0 | O1
-//                                         two S buffers per query tile, P over the buffer it came
-//                                         from: QK^T of key tile j+2 follows PV of key tile j in
-//                                         program order, so the scores of the NEXT key tile are
-//                                         already in tensor memory when a softmax warp finishes
-//                                         the current one, and a fast warp never waits for the
-//                                         slow warps of its tile
-// Options of the softmax warps:
-//   SPEC      from the second key tile on, the first 32 exponentials of a tile are computed against
-//             the running max of the PREVIOUS tiles while the row max of this tile is found in the
-//             same instruction stream; they stand whenever the max grew by less than 2^8 -- the
-//             condition under which O is not rescaled either -- and are recomputed otherwise, so
-//             nothing changes numerically
-//   PREFETCH  the next tile's scores are requested before this tile's P is handed over
+// Tensor memory (512 columns):
+//   P_ALIAS = false   S0 | S1 | O0 | O1 | P0 | P1   QK^T of the next key tile is issued once the
+//                                                   softmax warps have pulled S into registers (d = 64)
+//   P_ALIAS = true    S0/P0 | S1/P1 | O0 | O1       P overwrites the first half of the S columns it
+//                                                   came from; the next QK^T of that tile follows its
+//                                                   PV in program order (d = 128, where O takes 256 columns)
 // Every mbarrier wait is bounded; a wait that runs out records a code in `status` and the
 // whole CTA drains and frees its tensor memory.
 #pragma once
@@ -42,8 +30,10 @@
 
 namespace txb {
 
+// Section profile of this kernel: cycles per step, summed over key tiles, for one softmax lane of either
+// query tile ([0..15] tile 0, [32..47] tile 1) and the MMA lane ([16..31]).
 enum PairSection : int {
-    PSEC_SM_TOTAL = 0, PSEC_SM_WAIT_S = 1, PSEC_SM_LOAD_S = 2, PSEC_SM_MASK = 3, PSEC_SM_REDO = 4, PSEC_SM_EXP = 5,
+    PSEC_SM_TOTAL = 0, PSEC_SM_WAIT_S = 1, PSEC_SM_LOAD_S = 2, PSEC_SM_MASK = 3, PSEC_SM_EXP = 5,
     PSEC_SM_WAIT_PV = 6, PSEC_SM_STORE_P = 7, PSEC_SM_EPILOGUE = 9, PSEC_SM_TILES = 10,
     PSEC_MMA_TOTAL = 16, PSEC_MMA_WAIT_S = 17, PSEC_MMA_WAIT_K = 18, PSEC_MMA_WAIT_P = 19, PSEC_MMA_WAIT_V = 20,
     PSEC_MMA_ISSUE = 21,
@@ -51,18 +41,17 @@ enum PairSection : int {
 
 // POLY: bit e set = element e of every group of 16 exponentials is evaluated on the FMA pipe
 //       (bits come in pairs 2k, 2k+1: the polynomial works on two-wide fp32 vectors).
-// CHUNK_ST: P is stored 32 scores at a time as it is produced (false: once per tile, at the end).
-template <int D_, int BN_, int NS_, int POLY_, bool SPEC_, bool PREFETCH_, int LAYOUT_, bool PROF_ = false,
-          bool CHUNK_ST_ = false>
+// FAULT_TEST: the instantiation behind tx_selftest_wait_timeout -- every wait gives up after 2 ms instead of 2 s and
+//       the producer leaves out the K tile TcParams::skip_k_tile names, so that the give-up path can be exercised
+//       on a GPU without faulting or hanging anything.
+template <int D_, int BN_, int NS_, int POLY_, bool P_ALIAS_, bool PROF_ = false, bool FAULT_TEST_ = false>
 struct PairCfg {
-    static constexpr int D = D_, BN = BN_, NS = NS_, POLY = POLY_, LAYOUT = LAYOUT_;
-    static constexpr bool CHUNK_ST = CHUNK_ST_;
-    static constexpr bool P_ALIAS = LAYOUT_ != 0;            // P lives in S columns
-    static constexpr bool S2 = LAYOUT_ == 2;                 // two S buffers per query tile
-    static constexpr bool SPEC = SPEC_, PREFETCH = PREFETCH_ && LAYOUT_ != 1, PROF = PROF_;
+    static constexpr int D = D_, BN = BN_, NS = NS_, POLY = POLY_;
+    static constexpr bool P_ALIAS = P_ALIAS_, PROF = PROF_, FAULT_TEST = FAULT_TEST_;
+    static constexpr uint64_t WAIT_NS = FAULT_TEST_ ? 2000000ull : kWaitLimitNs;
     static constexpr int BM = 128;
     static constexpr int THREADS = 384;
-    static constexpr int REGS_LIGHT = 56, REGS_SOFTMAX = 224;   // 128 * 56 + 256 * 224 = 64512 <= 65536
+    static constexpr int REGS_LIGHT = 56, REGS_SOFTMAX = 224;   // 128 * 56 + 256 * 224 = 64512 <= 384 * 168
     static constexpr int KP = D / 64;                      // 64-column panels per row
     static constexpr uint32_t Q_TILE_BYTES = BM * D * 2;
     static constexpr uint32_t K_BYTES = BN * D * 2;
@@ -72,77 +61,21 @@ struct PairCfg {
     static constexpr uint32_t OFF_K = 2 * Q_TILE_BYTES;
     static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_V + NS * V_BYTES;
-    // q_full[2] s_full[2][2] s_free[2] p_full[2][2] pv_done[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
-    static constexpr int N_BARS = 14 + 4 * NS;
+    // q_full[2] s_full[2] s_free[2] p_full[2] pv_done[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
+    static constexpr int N_BARS = 10 + 4 * NS;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
     static constexpr uint32_t OFF_ABORT = OFF_TMEM + 4;
     static constexpr uint32_t SMEM_BYTES = ((OFF_ABORT + 4 + 127) / 128) * 128;
-    static constexpr int SBUF = S2 ? 2 : 1;                  // S buffers per query tile
-    static constexpr uint32_t COL_O0 = 2 * SBUF * BN, COL_O1 = COL_O0 + D;
-    static constexpr uint32_t COL_P_SEP = COL_O1 + D;        // LAYOUT 0: P0, then P1
-    static constexpr uint32_t COLS_USED = P_ALIAS ? COL_O1 + D : COL_P_SEP + BN;
+    static constexpr uint32_t COL_S0 = 0, COL_S1 = BN;
+    static constexpr uint32_t COL_O0 = 2 * BN, COL_O1 = 2 * BN + D;
+    static constexpr uint32_t COL_P0 = P_ALIAS ? COL_S0 : 2 * BN + 2 * D;
+    static constexpr uint32_t COL_P1 = P_ALIAS ? COL_S1 : 2 * BN + 2 * D + BN / 2;
+    static constexpr uint32_t COLS_USED = P_ALIAS ? 2 * BN + 2 * D : 3 * BN + 2 * D;
     static constexpr uint32_t TMEM_COLS = 512;
-    // column of S buffer `buf` of query tile t, and of the P that came from it
-    __host__ __device__ static constexpr uint32_t col_s(int t, int buf) { return (uint32_t)((t * SBUF + buf) * BN); }
-    __host__ __device__ static constexpr uint32_t col_p(int t, int buf)
-    {
-        return P_ALIAS ? col_s(t, buf) : COL_P_SEP + (uint32_t)(t * (BN / 2));
-    }
-    static_assert(D % 64 == 0 && BN % 32 == 0 && BN <= 256 && D <= 256, "tile shape");
+    static_assert(D % 64 == 0 && BN % 64 == 0 && BN <= 256 && D <= 256, "tile shape");
     static_assert(COLS_USED <= 512, "tensor memory has 512 columns");
     static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA may have");
-    static_assert(!S2 || NS >= 3, "with two S buffers the K ring runs two tiles ahead of the V ring");
 };
-
-// 32 scores of one query row, sv[C0 .. C0+32): p = 2^(s*scale - m) (a masked score is -inf and gives
-// exactly 0), rounded to fp16 pairs in `pk`, added into the two-wide fp32 sums.  With MAX_ALL the row
-// max of ALL BN raw scores of the tile is found in the same instruction stream (`mx`): the max runs
-// on the ALU pipe while the exponentials keep the special-function unit busy, so it costs no time
-// of its own.
-template <class Cfg, int C0, bool MAX_ALL>
-__device__ __forceinline__ void exp_chunk(const uint32_t (&sv)[Cfg::BN], uint32_t (&pk)[Cfg::CHUNK_ST ? 16 : Cfg::BN / 2],
-                                          float scale, float m,
-                                          float2 &sum_a, float2 &sum_b, float &mx)
-{
-    constexpr int BN = Cfg::BN, POLY = Cfg::POLY, CN = 32, MPI = BN / 8;   // MPI: scores per iteration for the max
-    const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m, -m);
-    float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = C0; i < C0 + CN; i += 4) {
-        const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2);
-        const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])), scale2, negm2);
-        const int e0 = i & 15;
-        const bool poly_a = (POLY >> e0) & 1, poly_b = (POLY >> (e0 + 2)) & 1;
-        const float2 ea = poly_a ? ptx::ex2_poly2(xa) : make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
-        const float2 eb = poly_b ? ptx::ex2_poly2(xb) : make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
-        sum_a = __fadd2_rn(sum_a, ea);
-        sum_b = __fadd2_rn(sum_b, eb);
-        constexpr int PK0 = Cfg::CHUNK_ST ? C0 : 0;      // chunked: pk holds this chunk only
-        pk[(i - PK0) / 2] = ptx::pack_half2(ea.x, ea.y);
-        pk[(i - PK0) / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
-        if constexpr (MAX_ALL) {
-            const int base = ((i - C0) / 4) * MPI;
-#pragma unroll
-            for (int e = 0; e < MPI; e += 2)
-                mxs[(e / 2) & 3] = ptx::max3(mxs[(e / 2) & 3], __uint_as_float(sv[base + e]), __uint_as_float(sv[base + e + 1]));
-        }
-    }
-    if constexpr (MAX_ALL) mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-}
-
-template <int BN>
-__device__ __forceinline__ float row_max(const uint32_t (&sv)[BN])
-{
-    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < BN; i += 8) {
-        mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-        mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
-        mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
-        mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
-    }
-    return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-}
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
@@ -155,11 +88,8 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t q_s = sbase + Cfg::OFF_Q, k_s = sbase + Cfg::OFF_K, v_s = sbase + Cfg::OFF_V;
     const uint32_t bar0 = sbase + Cfg::OFF_BAR;
     // per-tile barriers: index t = 0, 1
-    // s_full and p_full: one per S buffer, at + 8 * (2 * t + buf).  With two S buffers a softmax warp may be a
-    // whole key tile ahead of the MMA warp, so consecutive tiles must not share a barrier (a barrier that
-    // completes two phases before its waiter looks shows the old parity again).
-    const uint32_t q_full = bar0, s_full = bar0 + 16, s_free = bar0 + 48, p_full = bar0 + 64, pv_done = bar0 + 96;
-    const uint32_t k_full = bar0 + 112, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS, v_empty = v_full + 8 * NS;
+    const uint32_t q_full = bar0, s_full = bar0 + 16, s_free = bar0 + 32, p_full = bar0 + 48, pv_done = bar0 + 64;
+    const uint32_t k_full = bar0 + 80, k_empty = k_full + 8 * NS, v_full = k_empty + 8 * NS, v_empty = v_full + 8 * NS;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
@@ -201,11 +131,9 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         *abort_flag = 0;
         for (int t = 0; t < 2; ++t) {
             ptx::mbar_init(q_full + 8 * t, 1);
-            ptx::mbar_init(s_full + 8 * (2 * t), 1);
-            ptx::mbar_init(s_full + 8 * (2 * t + 1), 1);
+            ptx::mbar_init(s_full + 8 * t, 1);
             ptx::mbar_init(s_free + 8 * t, 4);          // one arrival per softmax warp of the tile
-            ptx::mbar_init(p_full + 8 * (2 * t), 4);
-            ptx::mbar_init(p_full + 8 * (2 * t + 1), 4);
+            ptx::mbar_init(p_full + 8 * t, 4);
             ptx::mbar_init(pv_done + 8 * t, 1);
         }
         for (int s = 0; s < NS; ++s) {
@@ -252,14 +180,17 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             for (int j = 0; j < n_max && ok; ++j) {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
-                ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag);
+                ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag, Cfg::WAIT_NS);
                 if (!ok) break;
+                const bool left_out = Cfg::FAULT_TEST && j == p.skip_k_tile;     // self-test: this tile never arrives
                 if (leader) {
-                    ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
+                    if (!left_out) {
+                        ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
 #pragma unroll
-                    for (int pn = 0; pn < Cfg::KP; ++pn)
-                        ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k, k_full + 8 * s,
-                                         pn * 64, j * BN, kvh);
+                        for (int pn = 0; pn < Cfg::KP; ++pn)
+                            ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k, k_full + 8 * s,
+                                             pn * 64, j * BN, kvh);
+                    }
                     if (j == 0 && n1 > 0) {
                         ptx::mbar_arrive_expect_tx(q_full + 8, Cfg::Q_TILE_BYTES);
 #pragma unroll
@@ -269,7 +200,7 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     }
                 }
                 __syncwarp();
-                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag);
+                ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag, Cfg::WAIT_NS);
                 if (!ok) break;
                 if (leader) {
                     ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
@@ -285,9 +216,8 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         // Warp-uniform control flow; one elected lane, the same one every time, issues the MMAs and
-        // the commits that track them.  The tensor pipe runs them in issue order, which is what the
-        // layouts with P in S columns rely on (a QK^T that overwrites a buffer follows the PV that
-        // read it).
+        // the commits that track them.  The tensor pipe runs them in issue order, which is what
+        // P_ALIAS relies on (the QK^T that overwrites S/P follows the PV that read P).
         if (run) {
             const bool leader = ptx::elect_one();
             constexpr uint32_t idesc_qk = ptx::idesc_f16(BM, BN, false);
@@ -299,18 +229,17 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             bool ok = true;
             tick_start();
             const long long t_begin = Cfg::PROF ? clock64() : 0;
-            // S_t(j) = Q_t K_j^T into S buffer j % SBUF; the K stage is released by whichever tile reads it last
+            // S_t = Q_t K_j^T; the K stage is released by whichever tile reads it last
             auto issue_qk = [&](int t, int j) -> bool {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
-                const int buf = Cfg::S2 ? (j & 1) : 0;
                 tick(0);
-                if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag)) return false;
+                if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag, Cfg::WAIT_NS)) return false;
                 tick(2);
                 ptx::tc_fence_after_sync();
                 const uint32_t ks_lo = k_lo + (uint32_t)s * (Cfg::K_BYTES >> 4);
                 const uint32_t qt_lo = q_lo + (uint32_t)t * (Cfg::Q_TILE_BYTES >> 4);
-                const uint32_t t_s = tmem + (uint32_t)((t * Cfg::SBUF + buf) * BN);
+                const uint32_t t_s = tmem + (t ? Cfg::COL_S1 : Cfg::COL_S0);
                 const bool last_reader = t == 1 ? true : (j >= n1);
                 if (leader) {
 #pragma unroll
@@ -321,27 +250,25 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                                     idesc_qk, kk > 0);
                     }
                     if (last_reader) ptx::mma_commit(k_empty + 8 * s);
-                    ptx::mma_commit(s_full + 8 * (2 * t + buf));
+                    ptx::mma_commit(s_full + 8 * t);
                 }
                 __syncwarp();
                 tick(5);
                 return true;
             };
-            // O_t += P_t(j) V_j
+            // O_t += P_t V_j
             auto issue_pv = [&](int t, int j) -> bool {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
-                const int buf = Cfg::S2 ? (j & 1) : 0;
                 tick(0);
-                if (!ptx::mbar_wait(v_full + 8 * s, ph, abort_flag)) return false;
+                if (!ptx::mbar_wait(v_full + 8 * s, ph, abort_flag, Cfg::WAIT_NS)) return false;
                 tick(4);
-                if (!ptx::mbar_wait(p_full + 8 * (2 * t + buf), (uint32_t)(Cfg::S2 ? (j >> 1) : j) & 1u, abort_flag)) return false;
+                if (!ptx::mbar_wait(p_full + 8 * t, (uint32_t)j & 1u, abort_flag, Cfg::WAIT_NS)) return false;
                 tick(3);
                 ptx::tc_fence_after_sync();
                 const uint32_t vs_lo = v_lo + (uint32_t)s * (Cfg::V_BYTES >> 4);
                 const uint32_t t_o = tmem + (t ? Cfg::COL_O1 : Cfg::COL_O0);
-                const uint32_t t_p = tmem + (Cfg::P_ALIAS ? (uint32_t)((t * Cfg::SBUF + buf) * BN)
-                                                          : Cfg::COL_P_SEP + (uint32_t)(t * (BN / 2)));
+                const uint32_t t_p = tmem + (t ? Cfg::COL_P1 : Cfg::COL_P0);
                 const bool last_reader = t == 1 ? true : (j >= n1);
                 if (leader) {
 #pragma unroll
@@ -356,35 +283,30 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 tick(5);
                 return true;
             };
-            // how far QK^T runs ahead of PV: with two S buffers, two key tiles
-            constexpr int AHEAD = Cfg::S2 ? 2 : 1;
-#pragma unroll
-            for (int a = 0; a < AHEAD; ++a) {
-                if (a < n0 && ok) {
-                    if (a == 0) ok = ptx::mbar_wait(q_full, 0, abort_flag);
-                    if (ok) ok = issue_qk(0, a);
-                }
-                if (a < n1 && ok) {
-                    if (a == 0) ok = ptx::mbar_wait(q_full + 8, 0, abort_flag);
-                    if (ok) ok = issue_qk(1, a);
-                }
+            if (n0 > 0) {
+                ok = ptx::mbar_wait(q_full, 0, abort_flag, Cfg::WAIT_NS);
+                if (ok) ok = issue_qk(0, 0);
+            }
+            if (ok && n1 > 0) {
+                ok = ptx::mbar_wait(q_full + 8, 0, abort_flag, Cfg::WAIT_NS);
+                if (ok) ok = issue_qk(1, 0);
             }
             for (int j = 0; j < n_max && ok; ++j) {
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     const int nt = t ? n1 : n0;
-                    if constexpr (Cfg::LAYOUT == 0) {
+                    if constexpr (!Cfg::P_ALIAS) {
                         if (j + 1 < nt && ok) {
                             tick(0);
-                            ok = ptx::mbar_wait(s_free + 8 * t, (uint32_t)j & 1u, abort_flag);
+                            ok = ptx::mbar_wait(s_free + 8 * t, (uint32_t)j & 1u, abort_flag, Cfg::WAIT_NS);
                             tick(1);
                             if (ok) { ptx::tc_fence_after_sync(); ok = issue_qk(t, j + 1); }
                         }
                         if (j < nt && ok) ok = issue_pv(t, j);
                     } else {
-                        // P(j) lives in an S buffer: the QK^T that reuses it follows this PV in program order
+                        // P_t lives in S_t's columns: the next QK^T of this tile follows its PV in program order
                         if (j < nt && ok) ok = issue_pv(t, j);
-                        if (j + AHEAD < nt && ok) ok = issue_qk(t, j + AHEAD);
+                        if (j + 1 < nt && ok) ok = issue_qk(t, j + 1);
                     }
                 }
             }
@@ -411,8 +333,11 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int row = q0t + r;
         const int nt = t ? n1 : n0;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem + lane_base + (t ? Cfg::COL_S1 : Cfg::COL_S0);
         const uint32_t t_o = tmem + lane_base + (t ? Cfg::COL_O1 : Cfg::COL_O0);
-        const uint32_t my_s_free = s_free + 8 * t, my_pv_done = pv_done + 8 * t;
+        const uint32_t t_p = tmem + lane_base + (t ? Cfg::COL_P1 : Cfg::COL_P0);
+        const uint32_t my_s_full = s_full + 8 * t, my_s_free = s_free + 8 * t, my_p_full = p_full + 8 * t,
+                       my_pv_done = pv_done + 8 * t;
         const float scale = p.scale_log2;
         float m_used = -1.0e30f;   // finite stand-in for "no key seen yet"
         float l = 0.f;
@@ -425,52 +350,21 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const bool prof_lane = prof_on && quarter == 0 && lane == 0;
         tick_start();
         const long long t_begin = Cfg::PROF ? clock64() : 0;
-        // O rescale for a tile whose running max moved, then P of that tile goes to the MMA warp.
-        float alpha_pend = 1.0f;
-        auto finish_tile = [&](int jj) {
-            if (jj > 0 && __any_sync(0xffffffffu, alpha_pend != 1.0f)) {
-                // Rare after the first tiles.  O may be touched once the previous PV is finished: with one
-                // S buffer that is already known (the P store waited for it, or S itself came after it).
-                if constexpr (Cfg::S2) {
-                    if (!ptx::mbar_wait(my_pv_done, (uint32_t)(jj - 1) & 1u, abort_flag)) ok = false;
-                    ptx::tc_fence_after_sync();
-                }
-#pragma unroll 1
-                for (int c = 0; c < D / 16; ++c) {
-                    uint32_t o[16];
-                    ptx::tmem_ld16(t_o + c * 16, o);
-                    ptx::tmem_wait_ld();
-                    ptx::reg_fence16(o);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_pend);
-                    ptx::tmem_st16(t_o + c * 16, o);
-                }
-            }
-            ptx::tmem_wait_st();
-            arrive_warp(p_full + 8 * (2 * t + (Cfg::S2 ? (jj & 1) : 0)));
-        };
         for (int j = 0; j < nt && ok; ++j) {
             const int kv0 = j * BN;
-            const int buf = Cfg::S2 ? (j & 1) : 0;
-            const uint32_t t_s = tmem + lane_base + (uint32_t)((t * Cfg::SBUF + buf) * BN);
-            const uint32_t t_p = Cfg::P_ALIAS ? t_s : tmem + lane_base + Cfg::COL_P_SEP + (uint32_t)(t * (BN / 2));
             tick(0);
-            ok = ptx::mbar_wait(s_full + 8 * (2 * t + buf), (uint32_t)(Cfg::S2 ? (j >> 1) : j) & 1u, abort_flag);
+            ok = ptx::mbar_wait(my_s_full, (uint32_t)j & 1u, abort_flag, Cfg::WAIT_NS);
             tick(PSEC_SM_WAIT_S);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            // this thread's score row travels to registers ...
+            // The whole score row goes to registers with one wait.  The array is defined here, inside the
+            // loop, by this one load: a row kept alive across the loop edge (loaded at the bottom for the
+            // next iteration) cost a register shuffle per tile and 20 % of the kernel's speed.
             uint32_t sv[BN];
             ptx::tmem_ld_cols<BN>(t_s, sv);
-            // ... while the previous tile's P lands and is handed over (PREFETCH)
-            if (Cfg::PREFETCH && j > 0) {
-                finish_tile(j - 1);
-                if (!ok) break;
-            }
-            tick(PSEC_SM_STORE_P);
             ptx::tmem_wait_ld();
             ptx::reg_fence_cols<BN>(sv);
-            if constexpr (Cfg::LAYOUT == 0) arrive_warp(my_s_free);   // S belongs to the MMA warp again
+            if constexpr (!Cfg::P_ALIAS) arrive_warp(my_s_free);   // S belongs to the MMA warp again
             tick(PSEC_SM_LOAD_S);
             const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0t));
             if (need_mask) {
@@ -482,79 +376,67 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
             }
             tick(PSEC_SM_MASK);
-            float mx = -INFINITY, m_cur = m_used, unused = 0.f;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BN; i += 8) {
+                mx0 = ptx::max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = ptx::max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                mx2 = ptx::max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                mx3 = ptx::max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_new = fmaxf(m_used, mx * scale);
+            const float m_next = (m_new > m_used + kLazyRescaleLog2) ? m_new : m_used;
+            const float alpha = ptx::ex2_approx(m_used - m_next);   // 1 when the max is kept
+            m_used = m_next;
+            // p = 2^(s*scale - m): a masked score is -inf and gives exactly 0
+            const float2 scale2 = make_float2(scale, scale), negm2 = make_float2(-m_next, -m_next);
             float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-            constexpr int PKN = Cfg::CHUNK_ST ? 16 : BN / 2;
-            uint32_t pk[PKN];
-            if (j == 0 || !Cfg::SPEC) {
-                // the row max has to be known first
-                mx = row_max<BN>(sv);
-                const float m_new = fmaxf(m_used, mx * scale);
-                if (m_new > m_used + kLazyRescaleLog2) m_cur = m_new;
-                exp_chunk<Cfg, 0, false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-            } else {
-                // First 32 exponentials against the running max of the earlier tiles, with this tile's row max
-                // found alongside.  They stand unless the max grew by more than 2^8 (the same condition under
-                // which O is rescaled) -- the first tiles of a row, as a rule -- and are recomputed otherwise.
-                exp_chunk<Cfg, 0, true>(sv, pk, scale, m_cur, sum_a, sum_b, mx);
-                const float m_new = fmaxf(m_cur, mx * scale);
-                const bool redo = m_new > m_cur + kLazyRescaleLog2;
-                if (__any_sync(0xffffffffu, redo)) {
-                    if (redo) m_cur = m_new;
-                    sum_a = make_float2(0.f, 0.f);
-                    sum_b = make_float2(0.f, 0.f);
-                    exp_chunk<Cfg, 0, false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                    tick(PSEC_SM_REDO);
-                }
-            }
-            if constexpr (Cfg::CHUNK_ST) {
-                if (Cfg::LAYOUT == 0 && j > 0) {
-                    // PV of the previous tile must be finished before P is overwritten (with P in S columns
-                    // the scores themselves came after it)
-                    ok = ptx::mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_flag);
-                    if (!ok) break;
-                    ptx::tc_fence_after_sync();
-                }
-                ptx::tmem_st16(t_p, pk);
+            uint32_t pk[BN / 2];
 #pragma unroll
-                for (int c = 1; c < BN / 32; ++c) {
-                    if (c == 1) exp_chunk<Cfg, 32, false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                    if (c == 2) exp_chunk<Cfg, (BN > 64 ? 64 : 0), false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                    if (c == 3) exp_chunk<Cfg, (BN > 96 ? 96 : 0), false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                    ptx::tmem_st16(t_p + c * 16, pk);
-                }
-            } else {
-                exp_chunk<Cfg, 32, false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                if constexpr (BN > 64) exp_chunk<Cfg, (BN > 64 ? 64 : 0), false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                if constexpr (BN > 96) exp_chunk<Cfg, (BN > 96 ? 96 : 0), false>(sv, pk, scale, m_cur, sum_a, sum_b, unused);
-                tick(PSEC_SM_EXP);
-                if (Cfg::LAYOUT == 0 && j > 0) {
-                    ok = ptx::mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_flag);
-                    if (!ok) break;
-                    ptx::tc_fence_after_sync();
-                }
-                tick(PSEC_SM_WAIT_PV);
-                if constexpr ((BN / 2) % 32 == 0) ptx::tmem_st_cols<BN / 2>(t_p, pk);
-                else {
-#pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) ptx::tmem_st16(t_p + c * 16, pk + c * 16);
-                }
+            for (int i = 0; i < BN; i += 4) {
+                const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2);
+                const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])), scale2, negm2);
+                const int e0 = i & 15;
+                const bool poly_a = (Cfg::POLY >> e0) & 1, poly_b = (Cfg::POLY >> (e0 + 2)) & 1;
+                const float2 ea = poly_a ? ptx::ex2_poly2(xa) : make_float2(ptx::ex2_approx(xa.x), ptx::ex2_approx(xa.y));
+                const float2 eb = poly_b ? ptx::ex2_poly2(xb) : make_float2(ptx::ex2_approx(xb.x), ptx::ex2_approx(xb.y));
+                sum_a = __fadd2_rn(sum_a, ea);
+                sum_b = __fadd2_rn(sum_b, eb);
+                pk[i / 2] = ptx::pack_half2(ea.x, ea.y);
+                pk[i / 2 + 1] = ptx::pack_half2(eb.x, eb.y);
             }
-            static_assert(BN == 64 || BN == 96 || BN == 128, "chunk schedule is written for 64-, 96- and 128-key tiles");
-            const float sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-            alpha_pend = ptx::ex2_approx(m_used - m_cur);   // 1 when the max is kept
-            l = l * alpha_pend + sum;
-            m_used = m_cur;
+            l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
             tick(PSEC_SM_EXP);
-            if constexpr (!Cfg::PREFETCH) {
-                finish_tile(j);
-                tick(PSEC_SM_STORE_P);
+            if (j > 0) {
+                // PV of the previous tile must be finished before P is overwritten or O rescaled (with P in
+                // S's columns the scores themselves came after it, so this wait returns at once)
+                ok = ptx::mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_flag, Cfg::WAIT_NS);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    // rare after the first tiles; 16 columns at a time
+#pragma unroll 1
+                    for (int c = 0; c < D / 16; ++c) {
+                        uint32_t o[16];
+                        ptx::tmem_ld16(t_o + c * 16, o);
+                        ptx::tmem_wait_ld();
+                        ptx::reg_fence16(o);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st16(t_o + c * 16, o);
+                    }
+                }
             }
+            tick(PSEC_SM_WAIT_PV);
+            ptx::tmem_st_cols<BN / 2>(t_p, pk);
+            ptx::tmem_wait_st();
+            arrive_warp(my_p_full);
+            tick(PSEC_SM_STORE_P);
         }
-        if (Cfg::PREFETCH && ok && nt > 0) finish_tile(nt - 1);
         const long long t_loop_end = Cfg::PROF ? clock64() : 0;
         if (run && nt > 0 && ok) {
-            ok = ptx::mbar_wait(my_pv_done, (uint32_t)(nt - 1) & 1u, abort_flag);
+            ok = ptx::mbar_wait(my_pv_done, (uint32_t)(nt - 1) & 1u, abort_flag, Cfg::WAIT_NS);
             if (ok) {
                 ptx::tc_fence_after_sync();
                 const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
@@ -622,6 +504,18 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag) {
+        // A wait ran out somewhere in this CTA (or in an earlier one of the launch): its rows are not valid.
+        // They are overwritten with NaN so that the failure is visible in the data, not only in the status word.
+        if (warp >= 4) {
+            const int ta = (warp - 4) >> 2, row_a = q0 + ta * BM + (warp & 3) * 32 + lane;
+            if (row_a < p.Sq) {
+                const size_t ob = ((size_t)bh * p.Sq + row_a) * p.dv_total;
+                for (int i = 0; i < D; ++i) {
+                    if (p.out_f16) static_cast<__half *>(p.out)[ob + i] = __ushort_as_half((unsigned short)0x7e00);
+                    else static_cast<float *>(p.out)[ob + i] = __int_as_float(0x7fc00000);
+                }
+            }
+        }
         for (int i = 0; i < 64; ++i) __nanosleep(2000);   // let copies in flight land
         __syncthreads();
     }

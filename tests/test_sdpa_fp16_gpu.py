@@ -256,15 +256,38 @@ def test_sharded_runs_equal_the_single_device_run_bitwise():
 
 
 def test_section_profile_entry_point():
-    """profile_sections_sdpa_* of the reference (csrc/tensor_ops.cpp:1434-1507): 32 counters, sane values."""
+    """Section profile of the tensor-core kernels (the fp16 counterpart of the reference's profile_sections_sdpa_*,
+    csrc/tensor_ops.cpp:1434-1507): 64 counters, sane values for both query tiles and the MMA lane."""
     from tensorax_b200 import _C
     B, H, S, d = 1, 2, 1024, 64
     q, k, v = (_C.from_numpy(seeded(90 + j, B, H, S, d).astype(np.float16), "cuda") for j in range(3))
     t = _C.profile_sections_sdpa(q, k, v)
-    assert len(t) == 32 and t[10] == S // 128                  # key tiles walked by CTA (0,0,0)
-    assert t[0] > 0 and t[16] > 0 and t[24] > 0                # softmax, MMA and producer lanes all reported
-    assert t[5] > t[3] > 0                                     # exponentials cost more than the row max
-    assert sum(t[1:9]) <= t[0] * 1.05
+    assert len(t) == 64 and t[10] == S // 128 and t[42] == S // 128     # key tiles walked by either query tile of CTA (0,0,0)
+    assert t[0] > 0 and t[32] > 0 and t[16] > 0                          # both softmax lanes and the MMA lane reported
+    assert t[5] > t[7] > 0 and t[37] > t[39] > 0                         # exponentials cost more than the P hand-over
+    assert sum(t[1:9]) <= t[0] * 1.05 and sum(t[33:41]) <= t[32] * 1.05
+
+
+@pytest.mark.parametrize("d", [256, 512])
+def test_section_profile_wide_heads(d):
+    """One query tile per CTA at d = 256 / 512: softmax, MMA and producer lanes report."""
+    from tensorax_b200 import _C
+    B, H, S = 1, 1, 512
+    q, k, v = (_C.from_numpy(seeded(95 + j, B, H, S, d).astype(np.float16), "cuda") for j in range(3))
+    t = _C.profile_sections_sdpa(q, k, v)
+    assert len(t) == 64 and t[10] == S // 64
+    assert t[0] > 0 and t[16] > 0 and t[24] > 0
+
+
+@pytest.mark.parametrize("name", ["naive", "tiled", "flash", "mma", "flash_optimized"])
+def test_fp32_section_profiles_by_reference_name(name):
+    """profile_sections_sdpa_{naive,tiled,flash,mma,flash_optimized} (csrc/tensor_ops.cpp:1434-1507,1622-1636):
+    32 clock64 stamps, non-decreasing over the eight sections the exact-fp32 kernel reports, the rest zero."""
+    from tensorax_b200 import _C
+    q, k, v = (_C.from_numpy(seeded(97 + j, 1, 2, 256, 64), "cuda") for j in range(3))
+    t = getattr(_C, f"profile_sections_sdpa_{name}")(q, k, v)
+    assert len(t) == 32 and all(x > 0 for x in t[:8]) and all(b >= a for a, b in zip(t[:8], t[1:8]))
+    assert all(x == 0 for x in t[8:])
 
 
 def test_non_blocking_python_calls_are_stream_ordered():
