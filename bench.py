@@ -17,7 +17,16 @@ barrier and for the max over ranks of the device time.
 Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events on the
 launching stream, inputs resident in HBM, L2 flushed between steps); `e2e` is
 the same metric through the host-buffer C-ABI call, pinned-host -> device copies
-and the device -> host copy of the result inside the timed region.
+and the device -> host copy of the result inside the timed region, with
+`copy_only_ms` = the same copy schedule with the kernels left out.  The line also
+carries
+  `sustained`  seconds of back-to-back launches of the same pass with the SM clock sampled
+               (the part runs into its power cap; `value` is the cool-part figure),
+  `strong`     ONE problem (BASELINE configs 4 and 2) cut by (batch, K/V head) units over the N
+               ranks with tensorax_b200.sharding.partition, each rank generating only its own
+               slab from per-(seed, tensor, head) streams; device time max over ranks, efficiency
+               against rank 0 running the whole problem alone, and a bitwise check of rank 0's slab,
+  `configs`    BASELINE configs 3, 4, 5 (d = 256, 512) and an fp32 shape, device-timed on rank 0.
 
 `--impl reference` times the reference's own CPU SDPA (oracle/_ref, or the C
 restatement if the reference library was not built) on all host cores, on a
@@ -50,7 +59,7 @@ PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel: mean of the two
 # launches captured with `ncu --set full` (137.14 MB, 136.12 MB)
 NCU_DRAM_BYTES_PER_LAUNCH = 136_630_000
-KERNEL_NAME = "sdpa_tc_kernel<DK=64,DV=64,BN=128,NS=3>"
+KERNEL_NAME = "sdpa_tc_pair_kernel<D=64,BN=128,NS=4> (two 128-row query tiles per CTA, one CTA per SM)"
 CPU_ROWS_PER_SLICE = 1024     # query rows per concurrent (b,h) slice in both CPU legs
 WORKLOAD = "config2: SDPA fwd fp16 (fp32 accumulate) B=4 H=8 S=8192 d=64 non-causal, no mask"
 

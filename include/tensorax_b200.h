@@ -72,6 +72,11 @@ TX_API int tx_cuda_set_device(int device);
  * cached in the pool (the reference pays a cudaMalloc/cudaFree pair per output tensor) */
 TX_API void *tx_cuda_malloc(size_t bytes);            /* NULL on failure */
 TX_API int tx_cuda_free(void *ptr);
+/* tx_cuda_malloc / tx_cuda_free are ordered on the legacy default stream: safe with work on stream NULL and on
+ * ordinary (blocking) streams, which synchronise with it.  A buffer last used by a kernel on a cudaStreamNonBlocking
+ * stream must be freed with tx_cuda_free_on(ptr, that_stream) (or after synchronising that stream): the block then
+ * returns to the pool in that stream's order.  No reference counterpart (its cuda_free is a synchronous cudaFree). */
+TX_API int tx_cuda_free_on(void *ptr, void *stream);
 TX_API int tx_cuda_pool_trim(void);                   /* give cached blocks back to the driver */
 TX_API int tx_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes);
 TX_API int tx_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes);
@@ -161,7 +166,11 @@ typedef struct tx_sdpa_desc {
 
 /* Enqueue one forward pass.  Query head h reads K/V head h / (q_heads/kv_heads). */
 TX_API int tx_sdpa_forward(const tx_sdpa_desc *desc);
-/* Wait for `stream` and report a kernel-side failure (bounded wait ran out), if any. */
+/* Wait for `stream` and report a kernel-side failure (bounded wait ran out), if any.  This is THE completion
+ * check of the asynchronous entry points (tx_sdpa_forward, tx_sdpa_backward, tx_linear_f32_cuda): a caller that
+ * synchronises some other way does not learn that a kernel gave up (its rows then read NaN).  The status word is one
+ * per device and stays set until a tx_sdpa_finish call on that device reports and clears it; launches issued in
+ * between return at once and write NaN. */
 TX_API int tx_sdpa_finish(void *stream);
 /* 1 if tx_sdpa_forward would run `desc` on the tcgen05 kernel, 0 if on CUDA cores. */
 TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
@@ -249,6 +258,10 @@ TX_API int tx_sdpa_backward(const tx_sdpa_bwd_desc *desc);
  *      and returns when `out` is complete.  Device staging buffers are cached in
  *      the library and reused between calls. */
 TX_API int tx_sdpa_forward_host(const tx_sdpa_desc *desc);
+/* The copy schedule of tx_sdpa_forward_host with the kernels left out (no reference counterpart): same chunks, same
+ * three streams, same bytes in both directions, `out` on the host receives whatever the device staging buffer holds.
+ * The benchmark times it beside the full call to show how much of the end-to-end time is the host <-> device path. */
+TX_API int tx_sdpa_forward_host_copies_only(const tx_sdpa_desc *desc);
 
 /* ---- allocation-free form (no counterpart in the reference).
  *

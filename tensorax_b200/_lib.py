@@ -24,7 +24,7 @@ TX_SDPA_F32_VIA_F16 = 8
 # every symbol include/tensorax_b200.h declares
 EXPORTED_SYMBOLS = (
     "tx_last_error", "tx_version",
-    "tx_cuda_is_available", "tx_cuda_device_count", "tx_cuda_set_device", "tx_cuda_malloc", "tx_cuda_free", "tx_cuda_pool_trim", "tx_cuda_memcpy_h2d",
+    "tx_cuda_is_available", "tx_cuda_device_count", "tx_cuda_set_device", "tx_cuda_malloc", "tx_cuda_free", "tx_cuda_free_on", "tx_cuda_pool_trim", "tx_cuda_memcpy_h2d",
     "tx_cuda_memcpy_d2h", "tx_cuda_memcpy_d2d", "tx_cuda_synchronize",
     "tx_host_alloc_pinned", "tx_host_free_pinned",
     "tx_sdpa_naive_cuda", "tx_sdpa_tiled_cuda", "tx_sdpa_flash_cuda",
@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_backward",
     "tx_sdpa_naive_profile_sections_cuda", "tx_sdpa_tiled_profile_sections_cuda", "tx_sdpa_flash_profile_sections_cuda",
     "tx_sdpa_mma_profile_sections_cuda", "tx_sdpa_optimized_flash_profile_sections_cuda",
-    "tx_selftest_wait_timeout",
+    "tx_selftest_wait_timeout", "tx_sdpa_forward_host_copies_only",
 )
 
 
@@ -88,6 +88,7 @@ def load():
     lib.tx_cuda_malloc.restype = c_void_p
     lib.tx_cuda_malloc.argtypes = [c_size_t]
     lib.tx_cuda_free.argtypes = [c_void_p]
+    lib.tx_cuda_free_on.argtypes = [c_void_p, c_void_p]
     for name in ("tx_cuda_memcpy_h2d", "tx_cuda_memcpy_d2h", "tx_cuda_memcpy_d2d"):
         getattr(lib, name).argtypes = [c_void_p, c_void_p, c_size_t]
     lib.tx_host_alloc_pinned.restype = c_void_p
@@ -108,6 +109,7 @@ def load():
     lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_selftest_wait_timeout.argtypes = [ctypes.POINTER(SdpaDesc), c_int32]
     lib.tx_sdpa_forward_host.argtypes = [ctypes.POINTER(SdpaDesc)]
+    lib.tx_sdpa_forward_host_copies_only.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_backward.argtypes = [ctypes.POINTER(SdpaBwdDesc)]
     lib.tx_sdpa_uses_tensor_cores.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_sdpa_finish.argtypes = [c_void_p]

@@ -46,6 +46,8 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
         (2, 4, 2, 300, 64, True, [300, 123]),
         (3, 2, 2, 257, 128, False, [5, 257, 100]),
         (2, 4, 2, 300, 64, True, None),
+        (1, 2, 1, 200, 256, True, [150]),          # wide heads: one query tile per CTA, Q in tensor memory
+        (1, 1, 1, 130, 512, False, None),          # two CTAs per query tile, each with half of the value columns
     ]
     for n, (B, Hq, Hkv, S, d, causal, lens) in enumerate(cases):
         q = seeded(700 + n, B, Hq, S, d).astype(np.float16)
