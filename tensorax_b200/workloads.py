@@ -33,6 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--d", type=int, default=128)
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--out-f16", action="store_true", help="fp16 result (TX_SDPA_OUT_F16)")
+    ap.add_argument("--fp32", action="store_true", help="float32 inputs: the exact-fp32 CUDA-core kernel (forward only)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seed", type=int, default=0)
@@ -44,12 +45,18 @@ def main(argv=None) -> int:
         raise RuntimeError("no CUDA device: this package has no CPU compute path")
     rng = np.random.default_rng(a.seed)
     nq, nk = B * H * S * D, B * Hkv * S * D
-    q, k, v = _randn_f16(rng, nq), _randn_f16(rng, nk), _randn_f16(rng, nk)
+    if a.fp32:
+        if a.what != "fwd":
+            raise SystemExit("--fp32 is a forward workload")
+        q, k, v = (_lib.to_device(rng.standard_normal(n, dtype=np.float32)) for n in (nq, nk, nk))
+    else:
+        q, k, v = _randn_f16(rng, nq), _randn_f16(rng, nk), _randn_f16(rng, nk)
     flags = _lib.TX_SDPA_OUT_F16 if a.out_f16 else 0
     out = _lib.DeviceBuffer(nq * (2 if a.out_f16 else 4))
     lse = _lib.DeviceBuffer(B * H * S * 4)
     fwd = _lib.SdpaDesc(q=q.ptr, k=k.ptr, v=v.ptr, mask=None, kv_lens=None, out=out.ptr, batch=B, q_heads=H,
-                        kv_heads=Hkv, seq_q=S, seq_k=S, d_k=D, d_v=D, dtype=_lib.TX_DTYPE_F16, causal=int(a.causal),
+                        kv_heads=Hkv, seq_q=S, seq_k=S, d_k=D, d_v=D,
+                        dtype=_lib.TX_DTYPE_F32 if a.fp32 else _lib.TX_DTYPE_F16, causal=int(a.causal),
                         flags=flags, stream=None, lse=lse.ptr if a.what == "bwd" else None)
     visible = 0.5 * S * (S + 1) if a.causal else float(S) * S
     if a.what == "fwd":
@@ -76,7 +83,7 @@ def main(argv=None) -> int:
         launch()
     _lib.check(lib.tx_sdpa_finish(None))
     ms = (time.perf_counter() - t0) / max(a.iters, 1) * 1e3
-    print(json.dumps({"workload": f"{a.what} fp16 B{B} Hq{H} Hkv{Hkv} S{S} d{D}" + (" causal" if a.causal else ""),
+    print(json.dumps({"workload": f"{a.what} {'fp32' if a.fp32 else 'fp16'} B{B} Hq{H} Hkv{Hkv} S{S} d{D}" + (" causal" if a.causal else ""),
                       "ms": ms, "tflops_algorithmic": flops / (ms * 1e-3) / 1e12, "iters": a.iters,
                       "kernels_launched": int(lib.tx_kernel_launch_count())}))
     return 0
