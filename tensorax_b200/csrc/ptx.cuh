@@ -124,6 +124,44 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, 
         : "memory");
 }
 
+// v when i < lim, else -inf: one compare and one select.  (Written as `if (!visible) v = -inf` over a register
+// array the compiler emitted a divergent branch per element: 27 cycles each on a causal diagonal tile.)
+__device__ __forceinline__ uint32_t keep_if_below(uint32_t v, int i, int lim)
+{
+    uint32_t r;
+    asm("{\n\t.reg .pred p;\n\tsetp.lt.s32 p, %2, %3;\n\tselp.b32 %0, %1, 0xff800000, p;\n\t}"
+        : "=r"(r) : "r"(v), "r"(i), "r"(lim));
+    return r;
+}
+
+// v when a < b, else 0 (same reason: a select, not a branch)
+__device__ __forceinline__ float zero_unless_lt(float v, int a, int b)
+{
+    float r;
+    asm("{\n\t.reg .pred p;\n\tsetp.lt.s32 p, %2, %3;\n\tselp.f32 %0, %1, 0f00000000, p;\n\t}"
+        : "=f"(r) : "f"(v), "r"(a), "r"(b));
+    return r;
+}
+
+// 3-D tile store from shared memory, tracked by the issuing thread's bulk async-group.  Elements of the box that
+// lie beyond the tensor's extent are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, uint32_t src, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Returns when all but the newest N of this thread's bulk groups have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // 4-D tile load: coordinates are (innermost element, row, plane, slab).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
                                             int c0, int c1, int c2, int c3)

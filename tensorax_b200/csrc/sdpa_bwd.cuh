@@ -321,6 +321,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             ptx::reg_fence_cols<CW>(dpv);
             arrive_warp(s_free);
             const bool need_mask = (kv0 + CW > kv_limit) || (p.causal && (kv0 + CW - 1 > q0));
+            const int lim = min(kv_limit - kv0, p.causal ? row - kv0 + 1 : CW);
             uint32_t pk[CW / 2];
             // packed fp32 pairs: x = s*c - lse, t = dP*scale - D*scale, dS = P*t
             const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse, -lse);
@@ -329,10 +330,9 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             for (int i = 0; i < CW; i += 2) {
                 const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), c2, nl2);
                 float2 pr = make_float2(ptx::ex2_approx(x.x), ptx::ex2_approx(x.y));
-                if (need_mask) {
-                    const int k0 = kv0 + i, k1 = k0 + 1;
-                    if (!(k0 < kv_limit && (!p.causal || k0 <= row))) pr.x = 0.f;
-                    if (!(k1 < kv_limit && (!p.causal || k1 <= row))) pr.y = 0.f;
+                if (need_mask) {                 // visible keys of this row are a prefix of the tile: [0, lim)
+                    pr.x = ptx::zero_unless_lt(pr.x, i, lim);
+                    pr.y = ptx::zero_unless_lt(pr.y, i + 1, lim);
                 }
                 const float2 tt = __ffma2_rn(make_float2(__uint_as_float(dpv[i]), __uint_as_float(dpv[i + 1])), s2, nd2);
                 const float2 ds = __fmul2_rn(pr, tt);
@@ -684,6 +684,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             arrive_warp(s_free);
             const int qc0 = qr0 + c0;               // first query of this warpgroup's columns
             const bool need_mask = p.causal && (key0 + BMK - 1 > qc0);
+            const int key_lo = key - qc0 - 1;
             uint32_t pp[CW / 2], pd[CW / 2];
             const float2 c2 = make_float2(p.scale_log2, p.scale_log2), s2 = make_float2(p.scale, p.scale);
 #pragma unroll
@@ -694,9 +695,9 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), c2, l2);
                 float2 pr = make_float2(ptx::ex2_approx(x.x), ptx::ex2_approx(x.y));
                 if (!key_ok) pr = make_float2(0.f, 0.f);
-                if (need_mask) {
-                    if (key > qc0 + i) pr.x = 0.f;
-                    if (key > qc0 + i + 1) pr.y = 0.f;
+                if (need_mask) {                 // query qc0 + i sees this key when key <= qc0 + i
+                    pr.x = ptx::zero_unless_lt(pr.x, key_lo, i);
+                    pr.y = ptx::zero_unless_lt(pr.y, key_lo, i + 1);
                 }
                 const float2 tt = __ffma2_rn(make_float2(__uint_as_float(dpv[i]), __uint_as_float(dpv[i + 1])), s2,
                                              dl);

@@ -52,6 +52,9 @@ struct TcParams {
     float scale_log2;         // (1/sqrt(d_k)) * log2(e)
     long long *prof;          // optional [64] cycle counters written by CTA (0,0,0) (section profile)
     int skip_k_tile;          // failure-path self-test instantiation only: the producer leaves this K tile out (-1 = none)
+    // sdpa_tc_pair_kernel only: the 1-D grid walks groups of `group` (batch, head) slabs; inside a group all
+    // slabs' longest work items come first (n_pairs = 256-row query pairs per slab, BH = slabs)
+    int group, n_pairs, BH;
 };
 
 // Section profile (the counterpart of the reference's TX_TICK clock64 sections,
@@ -503,12 +506,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
             const bool need_mask = (j * BN + BN > kv_limit) || (p.causal && (j * BN + BN - 1 > q0));
             if (need_mask) {
+                // visible keys of this row are a prefix of the tile: columns [0, lim)
+                const int lim = min(kv_limit - kv0, p.causal ? row - kv0 + 1 : BN);
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int col = kv0 + i;
-                    const bool vis = col < kv_limit && (!p.causal || col <= row);
-                    if (!vis) sv[i] = 0xff800000u;       // -inf
-                }
+                for (int i = 0; i < BN; ++i) sv[i] = ptx::keep_if_below(sv[i], i, lim);
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll

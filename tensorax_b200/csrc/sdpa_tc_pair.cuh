@@ -37,6 +37,12 @@ enum PairSection : int {
     PSEC_SM_WAIT_PV = 6, PSEC_SM_STORE_P = 7, PSEC_SM_EPILOGUE = 9, PSEC_SM_TILES = 10,
     PSEC_MMA_TOTAL = 16, PSEC_MMA_WAIT_S = 17, PSEC_MMA_WAIT_K = 18, PSEC_MMA_WAIT_P = 19, PSEC_MMA_WAIT_V = 20,
     PSEC_MMA_ISSUE = 21,
+    // from the CTA's first instruction: to the softmax lane's first score tile, to the end of its loop and of its
+    // epilogue; to the MMA lane's start (barriers and tensor memory set up), its Q tile and its first K tile
+    PSEC_SM_FIRST_S = 11, PSEC_SM_LOOP_END = 12, PSEC_SM_END = 13,
+    // inside the epilogue, from the end of the loop: the last PV has finished; the last result store is issued
+    PSEC_SM_EPI_PV = 14, PSEC_SM_EPI_SENT = 15,
+    PSEC_MMA_START = 22, PSEC_MMA_Q = 23, PSEC_MMA_K0 = 24,
 };
 
 // POLY: bit e set = element e of every group of 16 exponentials is evaluated on the FMA pipe
@@ -51,7 +57,7 @@ struct PairCfg {
     static constexpr uint64_t WAIT_NS = FAULT_TEST_ ? 2000000ull : kWaitLimitNs;
     static constexpr int BM = 128;
     static constexpr int THREADS = 384;
-    static constexpr int REGS_LIGHT = 56, REGS_SOFTMAX = 224;   // 128 * 56 + 256 * 224 = 64512 <= 384 * 168
+    static constexpr int REGS_LIGHT = 64, REGS_SOFTMAX = 216;   // 128 * 64 + 256 * 216 = 63488 <= 384 * 168 = 64512
     static constexpr int KP = D / 64;                      // 64-column panels per row
     static constexpr uint32_t Q_TILE_BYTES = BM * D * 2;
     static constexpr uint32_t K_BYTES = BN * D * 2;
@@ -60,7 +66,11 @@ struct PairCfg {
     static constexpr uint32_t OFF_Q = 0;
     static constexpr uint32_t OFF_K = 2 * Q_TILE_BYTES;
     static constexpr uint32_t OFF_V = OFF_K + NS * K_BYTES;
-    static constexpr uint32_t OFF_BAR = OFF_V + NS * V_BYTES;
+    // result staging of the epilogue: two 4 KB chunk buffers per softmax warp.  They live in the warp's quarter of
+    // its query tile's Q buffer; at D = 64 that quarter holds one, the other comes from here.
+    static constexpr uint32_t OFF_STAGE = OFF_V + NS * V_BYTES;
+    static constexpr uint32_t STAGE_BYTES = (Q_TILE_BYTES / 4 >= 8192) ? 0 : 8 * 4096;
+    static constexpr uint32_t OFF_BAR = OFF_STAGE + STAGE_BYTES;
     // q_full[2] s_full[2] s_free[2] p_full[2] pv_done[2] k_full[NS] k_empty[NS] v_full[NS] v_empty[NS]
     static constexpr int N_BARS = 10 + 4 * NS;
     static constexpr uint32_t OFF_TMEM = OFF_BAR + N_BARS * 8;
@@ -80,7 +90,8 @@ struct PairCfg {
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const TcParams p)
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                    const TcParams p)
 {
     constexpr int D = Cfg::D, BN = Cfg::BN, NS = Cfg::NS, BM = Cfg::BM;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -93,8 +104,9 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + Cfg::OFF_TMEM);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
+    const long long t_entry = Cfg::PROF ? clock64() : 0;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0;
     long long prof_last = 0;
     long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     auto tick = [&](int i) {
@@ -112,9 +124,16 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
     };
 
-    const int q_pair = (int)gridDim.x - 1 - (int)blockIdx.x;     // long (late) causal tiles first
+    // Work item of this CTA.  CTAs start in blockIdx order, so inside a group of `p.group` slabs the items are
+    // laid out longest first over ALL the group's slabs (late causal query pairs walk the most keys): the
+    // launch's last wave is then made of the shortest items.  A group is small enough for its K/V to stay in L2
+    // while the slabs' CTAs that share them run side by side.
+    const int span = p.group * p.n_pairs;
+    const int grp = (int)blockIdx.x / span, rem = (int)blockIdx.x % span;
+    const int slabs = min(p.group, p.BH - grp * p.group);
+    const int q_pair = p.n_pairs - 1 - rem / slabs;
     const int q0 = q_pair * (2 * BM);                            // first row of tile 0; tile 1 starts at q0 + BM
-    const int bh = blockIdx.y;
+    const int bh = grp * p.group + rem % slabs;
     const int b = bh / p.Hq, h = bh % p.Hq;
     const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
 
@@ -127,24 +146,63 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int n0 = (kv_end0 + BN - 1) / BN, n1 = (kv_end1 + BN - 1) / BN;
     const int n_max = max(n0, n1);
 
-    if (tid == 0) {
-        *abort_flag = 0;
-        for (int t = 0; t < 2; ++t) {
-            ptx::mbar_init(q_full + 8 * t, 1);
-            ptx::mbar_init(s_full + 8 * t, 1);
-            ptx::mbar_init(s_free + 8 * t, 4);          // one arrival per softmax warp of the tile
-            ptx::mbar_init(p_full + 8 * t, 4);
-            ptx::mbar_init(pv_done + 8 * t, 1);
+    // Warp 0 sets the barriers up and sends the first loads (both Q tiles, K and V of key tile 0) on their way
+    // before the CTA meets: the tensor-memory allocation, the meeting and the register hand-over then run
+    // under the loads' latency instead of in front of it.
+    const bool first_k_left_out = Cfg::FAULT_TEST && p.skip_k_tile == 0;
+    if (warp == 0) {
+        if (lane == 0) {
+            *abort_flag = 0;
+            for (int t = 0; t < 2; ++t) {
+                ptx::mbar_init(q_full + 8 * t, 1);
+                ptx::mbar_init(s_full + 8 * t, 1);
+                ptx::mbar_init(s_free + 8 * t, 4);          // one arrival per softmax warp of the tile
+                ptx::mbar_init(p_full + 8 * t, 4);
+                ptx::mbar_init(pv_done + 8 * t, 1);
+            }
+            for (int s = 0; s < NS; ++s) {
+                ptx::mbar_init(k_full + 8 * s, 1);
+                ptx::mbar_init(k_empty + 8 * s, 1);
+                ptx::mbar_init(v_full + 8 * s, 1);
+                ptx::mbar_init(v_empty + 8 * s, 1);
+            }
+            ptx::fence_mbar_init();
+            if (sbase & 1023u) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, TC_ERR_ALIGN);
+            } else if (n_max > 0) {
+                ptx::prefetch_tmap(&tm_q);
+                ptx::prefetch_tmap(&tm_k);
+                ptx::prefetch_tmap(&tm_v);
+                if (n0 > 0) {
+                    ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_TILE_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
+                }
+                if (!first_k_left_out) {
+                    ptx::mbar_arrive_expect_tx(k_full, Cfg::K_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(k_s + pn * Cfg::KV_PANEL, &tm_k, k_full, pn * 64, 0, kvh);
+                }
+                if (n1 > 0) {
+                    ptx::mbar_arrive_expect_tx(q_full + 8, Cfg::Q_TILE_BYTES);
+#pragma unroll
+                    for (int pn = 0; pn < Cfg::KP; ++pn)
+                        ptx::tma_load_3d(q_s + Cfg::Q_TILE_BYTES + pn * (BM * 128), &tm_q, q_full + 8, pn * 64,
+                                         q0 + BM, bh);
+                }
+                ptx::mbar_arrive_expect_tx(v_full, Cfg::V_BYTES);
+#pragma unroll
+                for (int pn = 0; pn < Cfg::KP; ++pn)
+                    ptx::tma_load_3d(v_s + pn * Cfg::KV_PANEL, &tm_v, v_full, pn * 64, 0, kvh);
+            }
+            // an earlier CTA of the launch may already have given up (asked after the loads are out: the answer
+            // takes a trip to global memory; the loads land during the teardown's grace period)
+            if (*reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;
         }
-        for (int s = 0; s < NS; ++s) {
-            ptx::mbar_init(k_full + 8 * s, 1);
-            ptx::mbar_init(k_empty + 8 * s, 1);
-            ptx::mbar_init(v_full + 8 * s, 1);
-            ptx::mbar_init(v_empty + 8 * s, 1);
-        }
-        ptx::fence_mbar_init();
-        if (sbase & 1023u) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_ALIGN); }
-        if (*reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;   // an earlier CTA already gave up
+        __syncwarp();
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), Cfg::TMEM_COLS);
@@ -164,18 +222,6 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // ------------------------------------------------------------ TMA producer
         if (run) {
             const bool leader = ptx::elect_one();
-            if (leader) {
-                ptx::prefetch_tmap(&tm_q);
-                ptx::prefetch_tmap(&tm_k);
-                ptx::prefetch_tmap(&tm_v);
-                if (n0 > 0) {
-                    ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_TILE_BYTES);
-#pragma unroll
-                    for (int pn = 0; pn < Cfg::KP; ++pn)
-                        ptx::tma_load_3d(q_s + pn * (BM * 128), &tm_q, q_full, pn * 64, q0, bh);
-                }
-            }
-            __syncwarp();
             bool ok = true;
             for (int j = 0; j < n_max && ok; ++j) {
                 const int s = j % NS;
@@ -183,7 +229,7 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 ok = ptx::mbar_wait(k_empty + 8 * s, ph ^ 1u, abort_flag, Cfg::WAIT_NS);
                 if (!ok) break;
                 const bool left_out = Cfg::FAULT_TEST && j == p.skip_k_tile;     // self-test: this tile never arrives
-                if (leader) {
+                if (leader && j > 0) {                                           // key tile 0 went out before the meeting
                     if (!left_out) {
                         ptx::mbar_arrive_expect_tx(k_full + 8 * s, Cfg::K_BYTES);
 #pragma unroll
@@ -191,18 +237,11 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                             ptx::tma_load_3d(k_s + s * Cfg::K_BYTES + pn * Cfg::KV_PANEL, &tm_k, k_full + 8 * s,
                                              pn * 64, j * BN, kvh);
                     }
-                    if (j == 0 && n1 > 0) {
-                        ptx::mbar_arrive_expect_tx(q_full + 8, Cfg::Q_TILE_BYTES);
-#pragma unroll
-                        for (int pn = 0; pn < Cfg::KP; ++pn)
-                            ptx::tma_load_3d(q_s + Cfg::Q_TILE_BYTES + pn * (BM * 128), &tm_q, q_full + 8, pn * 64,
-                                             q0 + BM, bh);
-                    }
                 }
                 __syncwarp();
                 ok = ptx::mbar_wait(v_empty + 8 * s, ph ^ 1u, abort_flag, Cfg::WAIT_NS);
                 if (!ok) break;
-                if (leader) {
+                if (leader && j > 0) {
                     ptx::mbar_arrive_expect_tx(v_full + 8 * s, Cfg::V_BYTES);
 #pragma unroll
                     for (int pn = 0; pn < Cfg::KP; ++pn)
@@ -229,12 +268,14 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             bool ok = true;
             tick_start();
             const long long t_begin = Cfg::PROF ? clock64() : 0;
+            long long t_q = 0, t_k0 = 0;
             // S_t = Q_t K_j^T; the K stage is released by whichever tile reads it last
             auto issue_qk = [&](int t, int j) -> bool {
                 const int s = j % NS;
                 const uint32_t ph = (uint32_t)(j / NS) & 1u;
                 tick(0);
                 if (!ptx::mbar_wait(k_full + 8 * s, ph, abort_flag, Cfg::WAIT_NS)) return false;
+                if constexpr (Cfg::PROF) { if (t_k0 == 0) t_k0 = clock64(); }
                 tick(2);
                 ptx::tc_fence_after_sync();
                 const uint32_t ks_lo = k_lo + (uint32_t)s * (Cfg::K_BYTES >> 4);
@@ -285,6 +326,7 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             };
             if (n0 > 0) {
                 ok = ptx::mbar_wait(q_full, 0, abort_flag, Cfg::WAIT_NS);
+                if constexpr (Cfg::PROF) t_q = clock64();
                 if (ok) ok = issue_qk(0, 0);
             }
             if (ok && n1 > 0) {
@@ -319,6 +361,9 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     p.prof[PSEC_MMA_WAIT_P] = prof_acc[3];
                     p.prof[PSEC_MMA_WAIT_V] = prof_acc[4];
                     p.prof[PSEC_MMA_ISSUE] = prof_acc[5];
+                    p.prof[PSEC_MMA_START] = t_begin - t_entry;
+                    p.prof[PSEC_MMA_Q] = t_q - t_entry;
+                    p.prof[PSEC_MMA_K0] = t_k0 - t_entry;
                 }
             }
         }
@@ -355,6 +400,7 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tick(0);
             ok = ptx::mbar_wait(my_s_full, (uint32_t)j & 1u, abort_flag, Cfg::WAIT_NS);
             tick(PSEC_SM_WAIT_S);
+            if constexpr (Cfg::PROF) { if (j == 0 && prof_lane) p.prof[(t ? 32 : 0) + PSEC_SM_FIRST_S] = clock64() - t_entry; }
             if (!ok) break;
             ptx::tc_fence_after_sync();
             // The whole score row goes to registers with one wait.  The array is defined here, inside the
@@ -368,12 +414,10 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tick(PSEC_SM_LOAD_S);
             const bool need_mask = (kv0 + BN > kv_limit) || (p.causal && (kv0 + BN - 1 > q0t));
             if (need_mask) {
+                // visible keys of this row are a prefix of the tile: columns [0, lim)
+                const int lim = min(kv_limit - kv0, p.causal ? row - kv0 + 1 : BN);
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const int col = kv0 + i;
-                    const bool vis = col < kv_limit && (!p.causal || col <= row);
-                    if (!vis) sv[i] = 0xff800000u;       // -inf
-                }
+                for (int i = 0; i < BN; ++i) sv[i] = ptx::keep_if_below(sv[i], i, lim);
             }
             tick(PSEC_SM_MASK);
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
@@ -437,43 +481,73 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const long long t_loop_end = Cfg::PROF ? clock64() : 0;
         if (run && nt > 0 && ok) {
             ok = ptx::mbar_wait(my_pv_done, (uint32_t)(nt - 1) & 1u, abort_flag, Cfg::WAIT_NS);
+            if constexpr (Cfg::PROF) { if (prof_lane) p.prof[(t ? 32 : 0) + PSEC_SM_EPI_PV] = clock64() - t_loop_end; }
             if (ok) {
                 ptx::tc_fence_after_sync();
                 const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
-                const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total;
-                float *orow = static_cast<float *>(p.out) + obase;
-                __half *orow_h = static_cast<__half *>(p.out) + obase;
                 if (p.lse && row < p.Sq) p.lse[(size_t)bh * p.Sq + row] = m_used + __log2f(l);
+                // O leaves through shared memory and one bulk tensor store per 128-byte-wide chunk of this warp's
+                // 32 rows: a thread owns a row, so direct stores would put 32 rows' 16-byte pieces into every
+                // store instruction.  The staging space is this warp's quarter of its own query tile's Q buffer
+                // (every QK^T of the tile has completed: the last s_full said so), written in the 128-byte
+                // swizzle the tensor map expects, which also keeps the 32 lanes on distinct banks.
+                constexpr uint32_t CHUNK_BYTES = 32 * 128;
+                const uint32_t buf_a = q_s + (uint32_t)t * Cfg::Q_TILE_BYTES + (uint32_t)quarter * (Cfg::Q_TILE_BYTES / 4);
+                const uint32_t buf_b = Cfg::STAGE_BYTES ? sbase + Cfg::OFF_STAGE + (uint32_t)(warp - 4) * CHUNK_BYTES
+                                                        : buf_a + CHUNK_BYTES;
+                const int row0 = q0t + quarter * 32;
+                const uint32_t my_line = (uint32_t)lane * 128u;
+                const uint32_t sw = (uint32_t)(lane & 7);
+                auto put = [&](uint32_t buf, int piece, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+                    ptx::st_shared_v4(buf + my_line + (((uint32_t)piece ^ sw) << 4), x, y, z, w);
+                };
+                auto send = [&](uint32_t buf, int col) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.Sq) {
+                        ptx::tma_store_3d(&tm_o, buf, col, row0, bh);
+                        ptx::tma_store_commit();
+                    }
+                };
+                // 64 columns of O per step: both loads first, then one chunk buffer each
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
-                    ptx::tmem_ld32(t_o + c * 32, o);
+                for (int c = 0; c < D / 64; ++c) {
+                    uint32_t o[32], o2[32];
+                    ptx::tmem_ld32(t_o + c * 64, o);
+                    ptx::tmem_ld32(t_o + c * 64 + 32, o2);
                     ptx::tmem_wait_ld();
                     ptx::reg_fence32(o);
-                    if (row < p.Sq) {
-                        if (p.out_f16) {
+                    ptx::reg_fence32(o2);
+                    if (p.out_f16) {
+                        const uint32_t buf = (c & 1) ? buf_b : buf_a;      // D / 64 <= 2 chunks: no buffer is used twice
+                        auto h2 = [&](uint32_t a, uint32_t b2) {
+                            return ptx::pack_half2(__uint_as_float(a) * inv_l, __uint_as_float(b2) * inv_l);
+                        };
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 hh;
-                                hh.x = ptx::pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                                hh.y = ptx::pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                                hh.z = ptx::pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                                hh.w = ptx::pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                                *reinterpret_cast<uint4 *>(orow_h + c * 32 + i) = hh;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 f;
-                                f.x = __uint_as_float(o[i]) * inv_l;
-                                f.y = __uint_as_float(o[i + 1]) * inv_l;
-                                f.z = __uint_as_float(o[i + 2]) * inv_l;
-                                f.w = __uint_as_float(o[i + 3]) * inv_l;
-                                *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
-                            }
+                        for (int i = 0; i < 32; i += 8) {
+                            put(buf, i / 8, h2(o[i], o[i + 1]), h2(o[i + 2], o[i + 3]), h2(o[i + 4], o[i + 5]),
+                                h2(o[i + 6], o[i + 7]));
+                            put(buf, 4 + i / 8, h2(o2[i], o2[i + 1]), h2(o2[i + 2], o2[i + 3]), h2(o2[i + 4], o2[i + 5]),
+                                h2(o2[i + 6], o2[i + 7]));
                         }
+                        send(buf, c * 64);
+                    } else {
+                        if (c > 0) {                                        // both buffers were sent in the step before
+                            if (lane == 0) ptx::tma_store_wait_read<0>();
+                            __syncwarp();
+                        }
+                        auto f = [&](uint32_t a) { return __float_as_uint(__uint_as_float(a) * inv_l); };
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) put(buf_a, i / 4, f(o[i]), f(o[i + 1]), f(o[i + 2]), f(o[i + 3]));
+                        send(buf_a, c * 64);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) put(buf_b, i / 4, f(o2[i]), f(o2[i + 1]), f(o2[i + 2]), f(o2[i + 3]));
+                        send(buf_b, c * 64 + 32);
                     }
                 }
+                if constexpr (Cfg::PROF) { if (prof_lane) p.prof[(t ? 32 : 0) + PSEC_SM_EPI_SENT] = clock64() - t_loop_end; }
+                if (lane == 0) ptx::tma_store_wait_read<0>();   // shared memory must outlive the stores' reads
+                __syncwarp();
             }
         }
         if (run && nt > 0 && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
@@ -483,6 +557,8 @@ sdpa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 dst[PSEC_SM_TOTAL] = t_loop_end - t_begin;
                 for (int i = 1; i <= 7; ++i) dst[i] = prof_acc[i];
                 dst[PSEC_SM_EPILOGUE] = clock64() - t_loop_end;
+                dst[PSEC_SM_LOOP_END] = t_loop_end - t_entry;
+                dst[PSEC_SM_END] = clock64() - t_entry;
                 dst[PSEC_SM_TILES] = nt;
             }
         }
