@@ -468,7 +468,7 @@ def run_ours(args, rank, world, local_rank, emit):
         one("c4", 8, 32, 8, 8192, 128, True, 1.0, 0.5, None, 5)
         one("c5_d256", 4, 8, 8, 4096, 256, False, 1.0 / 16.0, 1.0, None, 10)
         one("c5_d512", 4, 8, 8, 4096, 512, False, 1.0 / math.sqrt(512.0), 1.0, None, 10)
-        one("fp32_mha_shape", 4, 16, 16, 4096, 128, True, 1.0, 1.0, None, 3, dtype=torch.float32)
+        one("fp32_mha_shape", 4, 16, 16, 4096, 128, True, 1.0, 1.0, None, 10, dtype=torch.float32)
     barrier()
 
     if rank != 0:

@@ -46,7 +46,7 @@ enum { TX_DTYPE_F32 = 0, TX_DTYPE_F16 = 1 };
 
 /* flags of tx_sdpa_desc */
 enum {
-    TX_SDPA_FORCE_SIMT = 1,  /* use the CUDA-core kernel even where the tensor-core kernel applies */
+    TX_SDPA_FORCE_SIMT = 1,  /* use the exact CUDA-core kernel even where a tensor-core kernel applies (fp16 or fp32) */
     TX_SDPA_OUT_F16 = 4,     /* `out` is fp16 [batch, q_heads, seq_q, d_v] instead of fp32 (the reference only has fp32
                                 output, csrc/tensor_ops.cpp:1062; halves the result's bytes) */
     TX_SDPA_F32_VIA_F16 = 8, /* fp32 q/k/v: round them to fp16 on the device (pool temporaries, stream-ordered) and run the
@@ -91,7 +91,13 @@ TX_API int tx_host_free_pinned(void *ptr);
  *       sdpa_optimized_flash_cuda; kernels csrc/cuda/kernels/attn.cu:135-1111,1564-1615).
  *      Q [B,H,Sq,d_k], K [B,H,Sk,d_k], V [B,H,Sk,d_v], optional dense additive
  *      mask [B,H,Sq,Sk] (NULL = none), out [B,H,Sq,d_v], all fp32 on the device.
- *      Like the reference they return after the result is complete. */
+ *      Like the reference they return after the result is complete.
+ *      Two kernels stand behind the five names.  Calls without a dense mask and with d_k = d_v in {64, 128} run on
+ *      the tensor cores: every fp32 operand is carried as two fp16 numbers (hi + lo, 22 significand bits), every
+ *      product is three tcgen05 MMAs, tiles are summed in fp32 registers, the softmax is fp32 (within 2e-6 of the
+ *      reference's sdpa_cpu on unit-variance inputs, the figure of the exact kernel; 3e-5 at scores of +-100, where
+ *      the exact kernel itself is at 1e-5).  A device-side range check sends a call with |x| >= 2^15 or a
+ *      non-finite input to the exact CUDA-core kernel, which also takes every other shape and every dense mask. */
 TX_API int tx_sdpa_naive_cuda(const float *Q, const float *K, const float *V, const float *mask,
                               float *out, int64_t batch_size, int64_t num_heads,
                               int64_t seq_len_q, int64_t seq_len_k, int64_t d_k, int64_t d_v);
@@ -172,7 +178,8 @@ TX_API int tx_sdpa_forward(const tx_sdpa_desc *desc);
  * per device and stays set until a tx_sdpa_finish call on that device reports and clears it; launches issued in
  * between return at once and write NaN. */
 TX_API int tx_sdpa_finish(void *stream);
-/* 1 if tx_sdpa_forward would run `desc` on the tcgen05 kernel, 0 if on CUDA cores. */
+/* 1 if tx_sdpa_forward would run `desc` on a tcgen05 kernel (fp16, or fp32 as hi/lo fp16 pairs), 0 if on CUDA cores.
+ * (For fp32 the answer is about the shape: a value outside the pairs' range still sends the call to CUDA cores.) */
 TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
 /* How many kernels of this library have been launched by this process so far. */
 TX_API int64_t tx_kernel_launch_count(void);

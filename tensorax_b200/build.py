@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "libtensorax_b200.so")
 SOURCES = ["sdpa_api.cu"]
-HEADERS = ["ptx.cuh", "sdpa_simt.cuh", "sdpa_tc.cuh", "sdpa_tc_pair.cuh", "sdpa_bwd.cuh", "linear_simt.cuh", "linear_tc.cuh", os.path.join("..", "..", "include", "tensorax_b200.h")]
+HEADERS = ["ptx.cuh", "sdpa_simt.cuh", "sdpa_tc.cuh", "sdpa_tc_pair.cuh", "sdpa_tc_x3.cuh", "bounded_wait.h", "sdpa_bwd.cuh", "linear_simt.cuh", "linear_tc.cuh", os.path.join("..", "..", "include", "tensorax_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

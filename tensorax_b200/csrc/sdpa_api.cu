@@ -34,6 +34,7 @@
 #include "sdpa_simt.cuh"
 #include "sdpa_tc.cuh"
 #include "sdpa_tc_pair.cuh"
+#include "sdpa_tc_x3.cuh"
 #include "sdpa_bwd.cuh"
 
 namespace {
@@ -71,8 +72,20 @@ int ensure_device()
     return TX_OK;
 }
 
-// One status word per device, written by kernels whose bounded waits run out.
 constexpr int kMaxDevices = 64;
+int pool_ready();
+
+// Workspace of one call from the device's stream-ordered pool.  pool_ready() first: with the pool's default release
+// threshold of zero every synchronisation hands the freed workspace back to the driver, and the next call pays for
+// mapping it again (2.5 ms for 400 MB).
+int pool_alloc(char **p, size_t bytes, cudaStream_t st)
+{
+    if (int rc = pool_ready()) return rc;
+    TX_CUDA(cudaMallocAsync(reinterpret_cast<void **>(p), bytes, st));
+    return TX_OK;
+}
+
+// One status word per device, written by kernels whose bounded waits run out.
 int *g_status[kMaxDevices] = {};
 std::mutex g_status_mu;
 
@@ -453,7 +466,7 @@ int forward_f32_via_f16(const tx_sdpa_desc *d, cudaStream_t st)
                   nv = d->batch * d->kv_heads * d->seq_k * d->d_v;
     const size_t oq = 0, ok = align_up((size_t)nq * 2, 256), ov = ok + align_up((size_t)nk * 2, 256);
     char *ws = nullptr;
-    TX_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&ws), ov + (size_t)nv * 2, st));
+    if (int rc = pool_alloc(&ws, ov + (size_t)nv * 2, st)) return rc;
     const void *src[3] = {d->q, d->k, d->v};
     const int64_t n[3] = {nq, nk, nv};
     const size_t off[3] = {oq, ok, ov};
@@ -478,6 +491,105 @@ int forward_f32_via_f16(const tx_sdpa_desc *d, cudaStream_t st)
     return rc;
 }
 
+// fp32 in, fp32 out on the fp16 tensor cores (three products per GEMM, sdpa_tc_x3.cuh) for the calls that fit it.
+bool x3_eligible(const tx_sdpa_desc *d)
+{
+    if (d->dtype != TX_DTYPE_F32 || d->mask || d->lse) return false;
+    if (d->flags & (TX_SDPA_FORCE_SIMT | TX_SDPA_OUT_F16 | TX_SDPA_P_IN_SMEM)) return false;
+    if (d->d_k != d->d_v || (d->d_k != 64 && d->d_k != 128)) return false;
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al(d->q) || !al(d->k) || !al(d->v) || !al(d->out)) return false;
+    // the exact kernel stands behind it and must be launchable for the same call
+    if (d->batch * d->q_heads > 65535 || (d->seq_q + txb::SIMT_BR - 1) / txb::SIMT_BR > 65535) return false;
+    return true;
+}
+
+void fill_simt_params(txb::SimtParams *p, const tx_sdpa_desc *d)
+{
+    p->q = d->q; p->k = d->k; p->v = d->v;
+    p->mask = d->mask;
+    p->kv_lens = d->kv_lens;
+    p->out = d->out;
+    p->out_f16 = (d->flags & TX_SDPA_OUT_F16) ? 1 : 0;
+    p->B = d->batch; p->Hq = d->q_heads; p->Hkv = d->kv_heads;
+    p->Sq = d->seq_q; p->Sk = d->seq_k; p->dk = d->d_k; p->dv = d->d_v;
+    p->causal = d->causal ? 1 : 0;
+    p->scale = 1.0f / std::sqrt((float)d->d_k);
+    p->prof = nullptr;
+}
+
+template <class Cfg>
+int launch_x3_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+{
+    const int64_t nq = d->batch * d->q_heads * d->seq_q * d->d_k, nk = d->batch * d->kv_heads * d->seq_k * d->d_k;
+    // workspace: hi and lo fp16 copies of Q, K, V and the range flag, stream-ordered pool memory
+    const size_t bq = align_up((size_t)nq * 2, 256), bk = align_up((size_t)nk * 2, 256);
+    const size_t o_qh = 0, o_ql = bq, o_kh = 2 * bq, o_kl = o_kh + bk, o_vh = o_kl + bk, o_vl = o_vh + bk, o_flag = o_vl + bk;
+    char *ws = nullptr;
+    if (int rc = pool_alloc(&ws, o_flag + 256, st)) return rc;
+    int rc = TX_OK;
+    auto body = [&]() -> int {
+        int *flag = reinterpret_cast<int *>(ws + o_flag);
+        TX_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), st));
+        txb::SplitParams sp;
+        sp.seg[0] = {static_cast<const float *>(d->q), reinterpret_cast<__half *>(ws + o_qh), reinterpret_cast<__half *>(ws + o_ql), nq};
+        sp.seg[1] = {static_cast<const float *>(d->k), reinterpret_cast<__half *>(ws + o_kh), reinterpret_cast<__half *>(ws + o_kl), nk};
+        sp.seg[2] = {static_cast<const float *>(d->v), reinterpret_cast<__half *>(ws + o_vh), reinterpret_cast<__half *>(ws + o_vl), nk};
+        sp.flag = flag;
+        int sms = 0;
+        if (int r = sm_count(&sms)) return r;
+        const int64_t want = (std::max(nq, nk) / 4 + 255) / 256;
+        txb::split_f32_hi_lo_kernel<<<(unsigned)std::max<int64_t>(1, std::min<int64_t>(want, 16 * sms)), 256, 0, st>>>(sp);
+        g_launches++;
+        TX_CUDA(cudaGetLastError());
+
+        CUtensorMap qh, ql, kh, kl, vh, vl, to;
+        const int64_t sq = d->batch * d->q_heads, sk = d->batch * d->kv_heads;
+        if (int r = make_map(&qh, ws + o_qh, sq, d->seq_q, d->d_k, Cfg::BM)) return r;
+        if (int r = make_map(&ql, ws + o_ql, sq, d->seq_q, d->d_k, Cfg::BM)) return r;
+        if (int r = make_map(&kh, ws + o_kh, sk, d->seq_k, d->d_k, Cfg::BN)) return r;
+        if (int r = make_map(&kl, ws + o_kl, sk, d->seq_k, d->d_k, Cfg::BN)) return r;
+        if (int r = make_map(&vh, ws + o_vh, sk, d->seq_k, d->d_v, Cfg::BN)) return r;
+        if (int r = make_map(&vl, ws + o_vl, sk, d->seq_k, d->d_v, Cfg::BN)) return r;
+        if (int r = make_map(&to, d->out, sq, d->seq_q, d->d_v, 32, 4)) return r;
+        txb::X3Params p;
+        p.out = static_cast<float *>(d->out);
+        p.kv_lens = d->kv_lens;
+        p.out_of_range = flag;
+        p.status = status;
+        p.Hq = (int)d->q_heads; p.Hkv = (int)d->kv_heads; p.Sq = (int)d->seq_q; p.Sk = (int)d->seq_k;
+        p.causal = d->causal ? 1 : 0;
+        p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
+        const int64_t n_tiles = (d->seq_q + Cfg::BM - 1) / Cfg::BM;
+        int64_t group = 1;
+        if (d->causal && n_tiles <= 32) {
+            const int64_t want_g = std::min<int64_t>(sq, (2 * sms + n_tiles - 1) / n_tiles);
+            const int64_t n_groups = (sq + want_g - 1) / want_g;
+            group = (sq + n_groups - 1) / n_groups;
+        }
+        p.group = (int)group; p.n_tiles_q = (int)n_tiles; p.BH = (int)sq;
+        if (n_tiles * sq > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "SDPA: more than 2^31 work items");
+        if (int r = allow_smem(txb::sdpa_tc_x3_kernel<Cfg>, (int)Cfg::SMEM_BYTES)) return r;
+        txb::sdpa_tc_x3_kernel<Cfg><<<(unsigned)(n_tiles * sq), Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(qh, ql, kh, kl, vh, vl, to, p);
+        g_launches++;
+        TX_CUDA(cudaGetLastError());
+        // the exact kernel behind it: works only when the split pass found a value the fp16 pairs cannot carry
+        txb::SimtParams sp2;
+        fill_simt_params(&sp2, d);
+        sp2.only_if = flag;
+        return launch_simt<float>(sp2, st);
+    };
+    rc = body();
+    (void)cudaFreeAsync(ws, st);
+    return rc;
+}
+
+int launch_x3(const tx_sdpa_desc *d, cudaStream_t st, int *status)
+{
+    if (d->d_k == 64) return launch_x3_t<txb::X3Cfg<64, 4>>(d, st, status);
+    return launch_x3_t<txb::X3Cfg<128, 2>>(d, st, status);
+}
+
 int forward(const tx_sdpa_desc *d)
 {
     if (int rc = validate(d)) return rc;
@@ -493,17 +605,13 @@ int forward(const tx_sdpa_desc *d)
         if (int rc = status_word(&status)) return rc;
         return launch_tc(d, st, status);
     }
+    if (x3_eligible(d)) {
+        int *status = nullptr;
+        if (int rc = status_word(&status)) return rc;
+        return launch_x3(d, st, status);
+    }
     txb::SimtParams p;
-    p.q = d->q; p.k = d->k; p.v = d->v;
-    p.mask = d->mask;
-    p.kv_lens = d->kv_lens;
-    p.out = d->out;
-    p.out_f16 = (d->flags & TX_SDPA_OUT_F16) ? 1 : 0;
-    p.B = d->batch; p.Hq = d->q_heads; p.Hkv = d->kv_heads;
-    p.Sq = d->seq_q; p.Sk = d->seq_k; p.dk = d->d_k; p.dv = d->d_v;
-    p.causal = d->causal ? 1 : 0;
-    p.scale = 1.0f / std::sqrt((float)d->d_k);
-    p.prof = nullptr;
+    fill_simt_params(&p, d);
     return d->dtype == TX_DTYPE_F16 ? launch_simt<__half>(p, st) : launch_simt<float>(p, st);
 }
 
@@ -1064,7 +1172,7 @@ int tx_sdpa_backward(const tx_sdpa_bwd_desc *d)
     const int64_t rows = d->batch * d->q_heads * d->seq_q;
     const size_t h_bytes = align_up((size_t)rows * (size_t)d->d * 2, 256);
     char *ws = nullptr;
-    TX_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&ws), h_bytes + (size_t)rows * 4, st));
+    if (int rc = pool_alloc(&ws, h_bytes + (size_t)rows * 4, st)) return rc;
     __half *dout_h = reinterpret_cast<__half *>(ws);
     float *delta = reinterpret_cast<float *>(ws + h_bytes);
     const int warps = 8;
@@ -1107,7 +1215,7 @@ int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc)
         probe.dtype = TX_DTYPE_F16;
         return tc_eligible(&probe) ? 1 : 0;
     }
-    return tc_eligible(desc) ? 1 : 0;
+    return (tc_eligible(desc) || x3_eligible(desc)) ? 1 : 0;
 }
 
 int64_t tx_kernel_launch_count(void) { return g_launches.load(); }

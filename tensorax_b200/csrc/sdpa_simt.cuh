@@ -38,6 +38,8 @@ struct SimtParams {
     int out_f16;
     float scale;
     long long *prof;         // optional [32]: clock64 stamps of CTA (0,0,0), thread 0 (PROF instantiation only)
+    const int *only_if = nullptr;   // optional device word: the launch does nothing while it is 0 (this kernel as the
+                                    // stand-in behind a faster one that found it could not take the call)
 };
 
 // Stamps of the section profile (the counterpart of TX_TICK, tensorax csrc/cuda/profiling.cuh:20-51):
@@ -71,6 +73,7 @@ sdpa_simt_kernel(const SimtParams p)
                 p.prof[i] = clock64();
         }
     };
+    if (p.only_if && *reinterpret_cast<const volatile int *>(p.only_if) == 0) return;
     stamp(SIMT_T_START);
     __shared__ float q_s[SIMT_BR][SIMT_DKC + 1];
     __shared__ float k_s[SIMT_BC][SIMT_DKC + 1];
