@@ -57,7 +57,7 @@ ALG_BYTES_PER_STEP = B * H * S * D * (2 + 2 + 2 + 4)        # Q,K,V fp16 reads +
 METRIC = "fp16 SDPA fwd TFLOP/s per GPU at B4 H8 S8192 d64; % of B200 dense fp16 peak"
 PUBLISHED_TFLOPS = 24.73      # reference README.md:80-82, same config, RTX 3070 Ti Laptop (sm_86)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the config-2 kernel: mean of the two
-# launches captured with `ncu --set full` (133.78 MB, 133.83 MB)
+# launches captured with `ncu --set full` (138.21 MB, 138.04 MB)
 NCU_DRAM_BYTES_PER_LAUNCH = 138_200_000
 KERNEL_NAME = "sdpa_tc_pair_kernel<D=64,BN=128,NS=4> (two 128-row query tiles per CTA, one CTA per SM)"
 CPU_ROWS_PER_SLICE = 1024     # query rows per concurrent (b,h) slice in both CPU legs
