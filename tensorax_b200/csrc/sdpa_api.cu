@@ -318,7 +318,7 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     if (int rc = allow_smem(txb::sdpa_tc_kernel<Cfg>, (int)Cfg::SMEM_BYTES)) return rc;
     dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads),
               (unsigned)(d->d_v / Cfg::DV));
-    txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, to, p);
     g_launches++;
     TX_CUDA(cudaGetLastError());
     return TX_OK;

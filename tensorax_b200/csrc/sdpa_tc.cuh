@@ -150,7 +150,7 @@ constexpr float kLazyRescaleLog2 = 8.0f;
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS_PER_SM)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const TcParams p)
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const TcParams p)
 {
     constexpr int DK = Cfg::DK, DV = Cfg::DV, BN = Cfg::BN, NS = Cfg::NS, NSV = Cfg::NSV, BM = Cfg::BM;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -598,40 +598,70 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (ok) {
                 ptx::tc_fence_after_sync();
                 const float inv_l = 1.0f / l;    // l == 0 (no visible key) -> inf -> NaN rows, as the reference
-                const size_t obase = ((size_t)bh * p.Sq + row) * p.dv_total + dv0;
-                float *orow = static_cast<float *>(p.out) + obase;
-                __half *orow_h = static_cast<__half *>(p.out) + obase;
                 if (p.lse && dv0 == 0 && row < p.Sq) p.lse[(size_t)bh * p.Sq + row] = m_used + __log2f(l);
+                // O leaves through shared memory and one bulk tensor store per 128-byte-wide chunk of this warp's
+                // 32 rows (a thread owns a row: direct stores would put 32 rows' 16-byte pieces into every store
+                // instruction).  Staging: two 4 KB chunk buffers per warp in the K ring, which nothing uses any
+                // more (the last pv_done says every MMA has completed), written in the tensor map's 128-byte swizzle.
+                constexpr uint32_t CHUNK_BYTES = 32 * 128;
+                static_assert(NS * Cfg::K_BYTES >= 8 * CHUNK_BYTES, "staging space");
+                const int quarter = warp & 3;
+                const uint32_t buf_a = k_s + (uint32_t)quarter * (2 * CHUNK_BYTES), buf_b = buf_a + CHUNK_BYTES;
+                const int row0 = q0 + quarter * 32;
+                const uint32_t my_line = (uint32_t)lane * 128u;
+                const uint32_t sw = (uint32_t)(lane & 7);
+                auto put = [&](uint32_t buf, int piece, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+                    ptx::st_shared_v4(buf + my_line + (((uint32_t)piece ^ sw) << 4), x, y, z, w);
+                };
+                auto send = [&](uint32_t buf, int col) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.Sq) {
+                        ptx::tma_store_3d(&tm_o, buf, dv0 + col, row0, bh);
+                        ptx::tma_store_commit();
+                    }
+                };
+                auto reuse = [&](int step) {                        // both buffers were sent in the step before
+                    if (step > 0) {
+                        if (lane == 0) ptx::tma_store_wait_read<0>();
+                        __syncwarp();
+                    }
+                };
 #pragma unroll
-                for (int c = 0; c < DV / 32; ++c) {
-                    uint32_t o[32];
-                    ptx::tmem_ld32(t_o + c * 32, o);
+                for (int c = 0; c < DV / 64; ++c) {
+                    uint32_t o[32], o2[32];
+                    ptx::tmem_ld32(t_o + c * 64, o);
+                    ptx::tmem_ld32(t_o + c * 64 + 32, o2);
                     ptx::tmem_wait_ld();
                     ptx::reg_fence32(o);
-                    if (row < p.Sq) {
-                        if (p.out_f16) {
+                    ptx::reg_fence32(o2);
+                    if (p.out_f16) {
+                        const uint32_t buf = (c & 1) ? buf_b : buf_a;
+                        if ((c & 1) == 0) reuse(c);
+                        auto h2 = [&](uint32_t a, uint32_t b2) {
+                            return ptx::pack_half2(__uint_as_float(a) * inv_l, __uint_as_float(b2) * inv_l);
+                        };
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 h;
-                                h.x = ptx::pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                                h.y = ptx::pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                                h.z = ptx::pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                                h.w = ptx::pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                                *reinterpret_cast<uint4 *>(orow_h + c * 32 + i) = h;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 f;
-                                f.x = __uint_as_float(o[i]) * inv_l;
-                                f.y = __uint_as_float(o[i + 1]) * inv_l;
-                                f.z = __uint_as_float(o[i + 2]) * inv_l;
-                                f.w = __uint_as_float(o[i + 3]) * inv_l;
-                                *reinterpret_cast<float4 *>(orow + c * 32 + i) = f;
-                            }
+                        for (int i = 0; i < 32; i += 8) {
+                            put(buf, i / 8, h2(o[i], o[i + 1]), h2(o[i + 2], o[i + 3]), h2(o[i + 4], o[i + 5]),
+                                h2(o[i + 6], o[i + 7]));
+                            put(buf, 4 + i / 8, h2(o2[i], o2[i + 1]), h2(o2[i + 2], o2[i + 3]), h2(o2[i + 4], o2[i + 5]),
+                                h2(o2[i + 6], o2[i + 7]));
                         }
+                        send(buf, c * 64);
+                    } else {
+                        reuse(c);
+                        auto f = [&](uint32_t a) { return __float_as_uint(__uint_as_float(a) * inv_l); };
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) put(buf_a, i / 4, f(o[i]), f(o[i + 1]), f(o[i + 2]), f(o[i + 3]));
+                        send(buf_a, c * 64);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) put(buf_b, i / 4, f(o2[i]), f(o2[i + 1]), f(o2[i + 2]), f(o2[i + 3]));
+                        send(buf_b, c * 64 + 32);
                     }
                 }
+                if (lane == 0) ptx::tma_store_wait_read<0>();   // shared memory must outlive the stores' reads
+                __syncwarp();
             }
         }
         if (run && !ok) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_SOFTMAX); }
