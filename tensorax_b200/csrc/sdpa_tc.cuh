@@ -214,8 +214,26 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ptx::mbar_init(v_empty + 8 * s, 1);
         }
         ptx::fence_mbar_init();
-        if (sbase & 1023u) { *abort_flag = 1; atomicCAS(p.status, 0, TC_ERR_ALIGN); }
-        // another CTA of this (or an earlier, unchecked) launch already gave up: do not start
+        if (sbase & 1023u) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, TC_ERR_ALIGN);
+        } else if (n_tiles > 0) {
+            // The Q tile is requested before the CTA meets: the tensor-memory allocation and the meeting then
+            // run under the load's latency instead of in front of it.
+            ptx::prefetch_tmap(&tm_q);
+            ptx::prefetch_tmap(&tm_k);
+            ptx::prefetch_tmap(&tm_v);
+            ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int pn = 0; pn < Cfg::KP; ++pn) {
+                const uint32_t dst = (Cfg::Q_ALIAS && pn < Cfg::QP_TMEM)
+                                         ? k_s + pn * (BM * 128)                           // staged in the ring
+                                         : q_s + (pn - Cfg::QP_SKIP) * (BM * 128);
+                ptx::tma_load_3d(dst, &tm_q, q_full, pn * 64, q0, bh);
+            }
+        }
+        // another CTA of this (or an earlier, unchecked) launch already gave up: do not start (asked after the
+        // load is out: the answer takes a trip to global memory; the load lands during the teardown's grace period)
         if (*reinterpret_cast<volatile int *>(p.status) != 0) *abort_flag = 1;
     }
     if (warp == 1) {
@@ -235,20 +253,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // barrier handles stay in uniform registers); one elected lane issues the copies.
         if (run) {
             const bool leader = ptx::elect_one();
-            if (leader) {
-                ptx::prefetch_tmap(&tm_q);
-                ptx::prefetch_tmap(&tm_k);
-                ptx::prefetch_tmap(&tm_v);
-                ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-                for (int pn = 0; pn < Cfg::KP; ++pn) {
-                    const uint32_t dst = (Cfg::Q_ALIAS && pn < Cfg::QP_TMEM)
-                                             ? k_s + pn * (BM * 128)                           // staged in the ring
-                                             : q_s + (pn - Cfg::QP_SKIP) * (BM * 128);
-                    ptx::tma_load_3d(dst, &tm_q, q_full, pn * 64, q0, bh);
-                }
-            }
-            __syncwarp();
             bool ok = true;
             if constexpr (Cfg::Q_ALIAS) ok = ptx::mbar_wait(q_tmem, 0, abort_flag);   // the ring is free once Q has been copied out
             tick_start();
