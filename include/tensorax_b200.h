@@ -221,6 +221,10 @@ TX_API int tx_sdpa_optimized_flash_profile_sections_cuda(const float *Q, const f
  *        [+6] wait for the previous PV (+ O rescale), [+7] P store + hand-over, [+9] epilogue, [+10] key tiles;
  *        MMA lane: [16] loop total, [17] wait for S to be consumed, [18] wait for K, [19] wait for P,
  *        [20] wait for V, [21] MMA issue (blocks while the tensor pipe's queue is full).
+ *        The CTA's start and end, in cycles from its first instruction: softmax lane [+11] first score tile in hand,
+ *        [+12] end of the loop, [+13] end of the epilogue; from the end of the loop [+14] last PV finished,
+ *        [+15] last result store issued; MMA lane [22] started (barriers, tensor memory and the CTA-wide meeting
+ *        done), [23] Q tile 0 in shared memory, [24] first K tile in shared memory.
  *      d = 256, 512 (one query tile per CTA): softmax lane [0] loop total, [1] wait for S, [2] S -> registers,
  *        [3] mask + row max, [5] exponentials + pack + sum, [6] wait for the previous PV, [7] O rescale,
  *        [8] P store + hand-over, [9] epilogue, [10] key tiles; MMA lane [16] total, [17] wait for S to be consumed,
