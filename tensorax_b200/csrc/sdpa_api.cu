@@ -289,6 +289,9 @@ int launch_simt(const txb::SimtParams &p, cudaStream_t st)
 // polynomial at d = 64: two whole pairs of 16 (the polynomial is evaluated two-wide); measured round-robin
 // against 0, 1, 3 and 4 pairs of 8.
 constexpr int kPolyPairsD64 = 0x0303;
+// d = 128: one pair of 16 (0.896 -> 0.880 ms at B4 H8 S8192 against none, 0.884 with two pairs; the medians of
+// back-to-back runs move by 4-5 %: fewer special-function instructions also means a cooler part)
+constexpr int kPolyPairsD128 = 0x0003;
 
 template <class Cfg>
 int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
@@ -386,8 +389,8 @@ int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long
 // `prof` (section profile) selects the instrumented instantiation of the same shape.
 using PairD64 = txb::PairCfg<64, 128, 4, kPolyPairsD64, false>;
 using PairD64Prof = txb::PairCfg<64, 128, 4, kPolyPairsD64, false, true>;
-using PairD128 = txb::PairCfg<128, 128, 2, 0, true>;
-using PairD128Prof = txb::PairCfg<128, 128, 2, 0, true, true>;
+using PairD128 = txb::PairCfg<128, 128, 2, kPolyPairsD128, true>;
+using PairD128Prof = txb::PairCfg<128, 128, 2, kPolyPairsD128, true, true>;
 
 int launch_tc(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
 {
