@@ -191,8 +191,10 @@ TX_API int64_t tx_kernel_launch_count(void);
  *      thread 0 of CTA (0,0,0) of one instrumented launch (consecutive differences = section times, as with
  *      TX_TICK, csrc/cuda/profiling.cuh:20-51): [0] kernel entry, [1] first Q/K chunk staged, and for the
  *      first key tile [2] QK^T accumulated, [3] scores scaled/masked/parked, [4] online softmax done,
- *      [5] O updated; [6] all key tiles done, [7] output written; the rest stay 0.  All five names run the
- *      one exact-fp32 kernel, so they report the same sections.  Each call is also an NVTX range
+ *      [5] O updated; [6] all key tiles done, [7] output written; the rest stay 0.  All five names profile the
+ *      one exact-fp32 CUDA-core kernel, so they report the same sections -- also for a shape the launcher of
+ *      the same name would send to the fp32 tensor-core kernel (whose stages are those of the fp16 kernels:
+ *      tx_profile_sections_sdpa on an fp16 copy of the call shows them).  Each call is also an NVTX range
  *      ("sdpa.naive.profile", ...; the launchers themselves are "sdpa.naive", ..., "sdpa.mma.fp16"), as in
  *      the reference (csrc/cuda/profiling.cuh:7-18, csrc/cuda/kernels/attn.cu:973-1701). */
 TX_API int tx_sdpa_naive_profile_sections_cuda(const float *Q, const float *K, const float *V, const float *mask,
