@@ -469,6 +469,35 @@ def run_ours(args, rank, world, local_rank, emit):
         one("c5_d256", 4, 8, 8, 4096, 256, False, 1.0 / 16.0, 1.0, None, 10)
         one("c5_d512", 4, 8, 8, 4096, 512, False, 1.0 / math.sqrt(512.0), 1.0, None, 10)
         one("fp32_mha_shape", 4, 16, 16, 4096, 128, True, 1.0, 1.0, None, 10, dtype=torch.float32)
+
+        def one_bwd(name, Bp, Hq, Hkv, Sp, Dp, causal, steps, seed=13):
+            """The step after the path (tx_sdpa_backward: preprocess + dQ kernel + dK/dV kernel), rate on the
+            rule's five GEMMs = 2.5 x the forward's FLOPs."""
+            qq = unit_randn(torch, dev, seed, 0, 0, Bp * Hq, Sp, Dp, 1.0, torch.float16)
+            kk = unit_randn(torch, dev, seed, 1, 0, Bp * Hkv, Sp, Dp, 1.0, torch.float16)
+            vv = unit_randn(torch, dev, seed, 2, 0, Bp * Hkv, Sp, Dp, 1.0, torch.float16)
+            gg = unit_randn(torch, dev, seed, 3, 0, Bp * Hq, Sp, Dp, 1.0, torch.float32)
+            oo = torch.empty((Bp * Hq, Sp, Dp), dtype=torch.float32, device=dev)
+            ls = torch.empty((Bp * Hq, Sp), dtype=torch.float32, device=dev)
+            dq = torch.empty_like(oo)
+            dk = torch.empty((Bp * Hkv, Sp, Dp), dtype=torch.float32, device=dev)
+            dv = torch.empty_like(dk)
+            fd = make_desc(qq.data_ptr(), kk.data_ptr(), vv.data_ptr(), oo.data_ptr(), Bp, Hq, Hkv, Sp, Dp, causal=int(causal))
+            fd.lse = ls.data_ptr()
+            _lib.check(lib.tx_sdpa_forward(ctypes.byref(fd)))
+            _lib.check(lib.tx_sdpa_finish(sptr))
+            bd = _lib.SdpaBwdDesc(q=qq.data_ptr(), k=kk.data_ptr(), v=vv.data_ptr(), out=oo.data_ptr(), dout=gg.data_ptr(),
+                                  lse=ls.data_ptr(), kv_lens=None, dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
+                                  batch=Bp, q_heads=Hq, kv_heads=Hkv, seq_q=Sp, seq_k=Sp, d=Dp, causal=int(causal), flags=0,
+                                  stream=sptr)
+            t = time_launches(lambda: _lib.check(lib.tx_sdpa_backward(ctypes.byref(bd))), steps)
+            alg = 10.0 * Hq * Dp * visible_scores(Sp, causal, None, Bp)
+            configs[name] = {"ms": t, "tflops_algorithmic": alg / (t * 1e-3) / 1e12,
+                             "frac_of_measured_peak": alg / (t * 1e-3) / 1e12 / peak_b, "tensor_cores": True,
+                             "what": "backward of the SDPA rule: dQ, dK, dV"}
+
+        one_bwd("bwd_c3_shape", 4, 16, 16, 4096, 128, True, 5)
+        one_bwd("bwd_d64", 4, 8, 8, 8192, 64, False, 5)
     barrier()
 
     if rank != 0:
