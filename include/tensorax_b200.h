@@ -269,7 +269,9 @@ TX_API int tx_sdpa_backward(const tx_sdpa_bwd_desc *desc);
 /* ---- host-buffer form (no reference counterpart): `desc` holds HOST pointers
  *      (q, k, v, kv_lens, out; mask must be NULL).  Copies in, runs, copies out,
  *      and returns when `out` is complete.  Device staging buffers are cached in
- *      the library and reused between calls. */
+ *      the library and reused between calls.  With pinned buffers (tx_host_alloc_pinned) uploads, kernels and
+ *      the way back overlap in chunks of whole (batch, head) units, and the results are written into `out` by a
+ *      small kernel (the device addresses pinned memory directly); pageable buffers work too, through staged copies. */
 TX_API int tx_sdpa_forward_host(const tx_sdpa_desc *desc);
 /* The copy schedule of tx_sdpa_forward_host with the kernels left out (no reference counterpart): same chunks, same
  * three streams, same bytes in both directions, `out` on the host receives whatever the device staging buffer holds.
