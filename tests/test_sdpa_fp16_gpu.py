@@ -237,6 +237,36 @@ def test_host_buffer_entry_point():
     assert _lib.load().tx_sdpa_forward_host(ctypes.byref(desc)) == 5          # TX_ERR_UNSUPPORTED, nothing ran
 
 
+def test_host_buffer_entry_point_with_pinned_buffers():
+    """Pinned buffers: the call is cut into chunks (the problem is above the 8 MiB it takes) and every chunk's result is
+    written into the caller's buffer by a kernel.  Same bits as the device-resident call."""
+    lib = _lib.load()
+    B, Hq, Hkv, S, d = 3, 4, 2, 2048, 64
+    q = seeded(75, B, Hq, S, d).astype(np.float16)
+    k, v = (seeded(76 + j, B, Hkv, S, d).astype(np.float16) for j in range(2))
+    n_out = B * Hq * S * d
+    sizes = [q.nbytes, k.nbytes, v.nbytes, n_out * 4]
+    ptrs = [lib.tx_host_alloc_pinned(n) for n in sizes]
+    assert all(ptrs)
+    try:
+        for ptr, a in zip(ptrs[:3], (q, k, v)):
+            ctypes.memmove(ptr, a.ctypes.data, a.nbytes)
+        ctypes.memset(ptrs[3], 0xFF, sizes[3])
+        desc = _lib.SdpaDesc(q=ptrs[0], k=ptrs[1], v=ptrs[2], mask=None, kv_lens=None, out=ptrs[3], batch=B, q_heads=Hq,
+                             kv_heads=Hkv, seq_q=S, seq_k=S, d_k=d, d_v=d, dtype=_lib.TX_DTYPE_F16, causal=1, flags=0,
+                             stream=None)
+        n0 = lib.tx_kernel_launch_count()
+        _lib.check(lib.tx_sdpa_forward_host(ctypes.byref(desc)))
+        launches = lib.tx_kernel_launch_count() - n0
+        out = np.ctypeslib.as_array((ctypes.c_float * n_out).from_address(ptrs[3])).reshape(B, Hq, S, d).copy()
+    finally:
+        for ptr in ptrs:
+            lib.tx_host_free_pinned(ptr)
+    dev, _ = sdpa_device(q, k, v, causal=True)
+    assert np.array_equal(out.view(np.uint32), dev.view(np.uint32))
+    assert launches >= 4 and launches % 2 == 0          # per chunk: one attention launch and one write-back launch
+
+
 def test_sharded_runs_equal_the_single_device_run_bitwise():
     """Each rank's slab through the same kernel, reassembled: identical bits."""
     from tensorax_b200 import sharding
