@@ -59,6 +59,22 @@ def test_long_sequence_stays_fp32_grade(d):
     assert float(err) <= 2e-6, f"max-abs {float(err):.2e}"
 
 
+def test_full_size_parity_shape_sampled():
+    """The fp32 shape of MultiHeadAttention's parity configuration (B4 H16 S4096 d128, causal) at full size: sampled
+    heads and row blocks (first, diagonal-crossing middle, last) against the oracle."""
+    B, H, S, d = 4, 16, 4096, 128
+    q, k, v = seeded(41, B, H, S, d), seeded(42, B, H, S, d), seeded(43, B, H, S, d)
+    got, tc = sdpa_device(q, k, v, causal=True)
+    assert tc
+    worst = 0.0
+    for bh in (0, 21, 42, 63):
+        for r0 in (0, 1984, S - 128):
+            ref = oracle.sdpa_structured(q, k, v, causal=True, heads=[bh], rows=(r0, r0 + 128))
+            b, h = divmod(bh, H)
+            worst = max(worst, float(np.abs(got[b, h, r0:r0 + 128] - ref[b, h, r0:r0 + 128]).max()))
+    assert worst <= 5e-6, f"max-abs {worst:.2e}"
+
+
 @pytest.mark.parametrize("bad", [1.0e6, -4.0e4, np.inf, np.nan])
 def test_value_outside_the_pairs_range_goes_to_the_exact_kernel(bad):
     d = 64
