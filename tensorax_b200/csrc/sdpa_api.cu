@@ -327,6 +327,25 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     return TX_OK;
 }
 
+// Slabs per group of the launch order of a causal call (see launch_pair_t); 1 = slab-major.
+int causal_group(const tx_sdpa_desc *d, int64_t items_per_slab, int64_t *group)
+{
+    *group = 1;
+    const int64_t slabs = d->batch * d->q_heads;
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    if (!d->causal || slabs <= 1 || items_per_slab * slabs > 16 * (int64_t)sms) return TX_OK;
+    const int64_t ratio = d->q_heads / d->kv_heads;
+    const double kv_bytes_per_slab = 2.0 * (double)d->seq_k * (double)(d->d_k + d->d_v) / (double)ratio;
+    const int64_t by_l2 = std::max<int64_t>(1, (int64_t)(48.0 * 1048576.0 / kv_bytes_per_slab));
+    const int64_t two_waves = (2 * sms + items_per_slab - 1) / items_per_slab;
+    const int64_t want = std::min<int64_t>(slabs, std::max(by_l2, two_waves));
+    const int64_t n_groups = (slabs + want - 1) / want;
+    const int64_t g = (slabs + n_groups - 1) / n_groups;          // equal groups, none left small at the end
+    *group = std::min<int64_t>(slabs, (g + ratio - 1) / ratio * ratio);
+    return TX_OK;
+}
+
 template <class Cfg>
 int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr, int skip_k_tile = -1)
 {
@@ -353,21 +372,19 @@ int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long
     p.prof = prof;
     p.skip_k_tile = skip_k_tile;
     // Work items in launch order.  Slab-major (group = 1: a slab's CTAs, which share its K/V, start side by side)
-    // unless the mask is causal and a slab has few query pairs: then the slabs are taken in groups of about two
-    // waves of CTAs, and inside a group every slab's longest items come before any shorter one, so that the SMs
-    // do not end on a late slab's long items.  Measured on B200: S = 2048 / 4096 causal 3 % / 2.5 % faster
-    // grouped; at 32 pairs per slab (S = 8192) a slab's own longest-first order already mixes long and short
-    // items and grouping was 4 % slower.
+    // unless the mask is causal: then the slabs are taken in groups, and inside a group every slab's longest items
+    // come before any shorter one, so that the SMs do not end on a late slab's long items.  A group is as large as
+    // its K/V may be while staying in L2 (48 MB; K/V heads shared by several query heads count once), at least two
+    // waves of CTAs, a whole number of K/V heads, and the groups are equal (a small last group is the same tail
+    // again: 32 slabs as 10 + 10 + 10 + 2 were slower than slab-major, as 4 x 8 or as one group 12-24 % faster).
+    // Measured on B200, causal, slab-major -> grouped: d = 128 B1 Hq32 Hkv8 S8192 0.514 -> 0.468 ms, B1 H16 S8192
+    // 0.333 -> 0.253, d = 64 B4 H8 S8192 0.388 -> 0.342, B4 H16 S4096 d = 128 0.286 -> 0.268, d = 64 0.220 -> 0.199,
+    // B8 H16 S2048 0.170 -> 0.162.  A launch of more than 16 waves keeps the slab-major order: its tail is small
+    // whatever the order, and the order that shares K/V best wins (B8 Hq32 Hkv8 S8192, 55 waves: 3.78 against 3.98 ms).
     const int64_t n_pairs = (d->seq_q + 2 * Cfg::BM - 1) / (2 * Cfg::BM);
     const int64_t slabs = d->batch * d->q_heads;
     int64_t group = 1;
-    if (d->causal && n_pairs <= 16) {
-        int sms = 0;
-        if (int rc = sm_count(&sms)) return rc;
-        const int64_t want = std::min<int64_t>(slabs, (2 * sms + n_pairs - 1) / n_pairs);
-        const int64_t n_groups = (slabs + want - 1) / want;
-        group = (slabs + n_groups - 1) / n_groups;            // equal groups, none left small at the end
-    }
+    if (int rc = causal_group(d, n_pairs, &group)) return rc;
     p.group = (int)group;
     p.n_pairs = (int)n_pairs;
     p.BH = (int)slabs;
@@ -566,11 +583,7 @@ int launch_x3_t(const tx_sdpa_desc *d, cudaStream_t st, int *status)
         p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
         const int64_t n_tiles = (d->seq_q + Cfg::BM - 1) / Cfg::BM;
         int64_t group = 1;
-        if (d->causal && n_tiles <= 32) {
-            const int64_t want_g = std::min<int64_t>(sq, (2 * sms + n_tiles - 1) / n_tiles);
-            const int64_t n_groups = (sq + want_g - 1) / want_g;
-            group = (sq + n_groups - 1) / n_groups;
-        }
+        if (int r = causal_group(d, n_tiles, &group)) return r;
         p.group = (int)group; p.n_tiles_q = (int)n_tiles; p.BH = (int)sq;
         if (n_tiles * sq > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "SDPA: more than 2^31 work items");
         if (int r = allow_smem(txb::sdpa_tc_x3_kernel<Cfg>, (int)Cfg::SMEM_BYTES)) return r;
