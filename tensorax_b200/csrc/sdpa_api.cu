@@ -334,7 +334,7 @@ int causal_group(const tx_sdpa_desc *d, int64_t items_per_slab, int64_t *group)
     const int64_t slabs = d->batch * d->q_heads;
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
-    if (!d->causal || slabs <= 1 || items_per_slab * slabs > 16 * (int64_t)sms) return TX_OK;
+    if (!d->causal || slabs <= 1) return TX_OK;
     const int64_t ratio = d->q_heads / d->kv_heads;
     const double kv_bytes_per_slab = 2.0 * (double)d->seq_k * (double)(d->d_k + d->d_v) / (double)ratio;
     const int64_t by_l2 = std::max<int64_t>(1, (int64_t)(48.0 * 1048576.0 / kv_bytes_per_slab));
@@ -379,8 +379,7 @@ int launch_pair_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long
     // again: 32 slabs as 10 + 10 + 10 + 2 were slower than slab-major, as 4 x 8 or as one group 12-24 % faster).
     // Measured on B200, causal, slab-major -> grouped: d = 128 B1 Hq32 Hkv8 S8192 0.514 -> 0.468 ms, B1 H16 S8192
     // 0.333 -> 0.253, d = 64 B4 H8 S8192 0.388 -> 0.342, B4 H16 S4096 d = 128 0.286 -> 0.268, d = 64 0.220 -> 0.199,
-    // B8 H16 S2048 0.170 -> 0.162.  A launch of more than 16 waves keeps the slab-major order: its tail is small
-    // whatever the order, and the order that shares K/V best wins (B8 Hq32 Hkv8 S8192, 55 waves: 3.78 against 3.98 ms).
+    // B8 H16 S2048 0.170 -> 0.162; long launches gain less but gain (B8 Hq32 Hkv8 S8192, 55 waves: 3.80 -> 3.73 ms).
     const int64_t n_pairs = (d->seq_q + 2 * Cfg::BM - 1) / (2 * Cfg::BM);
     const int64_t slabs = d->batch * d->q_heads;
     int64_t group = 1;
