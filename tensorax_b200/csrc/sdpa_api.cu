@@ -327,23 +327,28 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     return TX_OK;
 }
 
-// Slabs per group of the launch order of a causal call (see launch_pair_t); 1 = slab-major.
-int causal_group(const tx_sdpa_desc *d, int64_t items_per_slab, int64_t *group)
+// Slabs per group of the launch order of a causal call (see launch_two_tiles); 1 = slab-major.  `bytes_per_slab`: what
+// the CTAs of one slab stream through L2; `multiple`: slabs that share those bytes and should stay together.
+int launch_group(bool causal, int64_t slabs, int64_t items_per_slab, double bytes_per_slab, int64_t multiple, int64_t *group)
 {
     *group = 1;
-    const int64_t slabs = d->batch * d->q_heads;
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
-    if (!d->causal || slabs <= 1) return TX_OK;
-    const int64_t ratio = d->q_heads / d->kv_heads;
-    const double kv_bytes_per_slab = 2.0 * (double)d->seq_k * (double)(d->d_k + d->d_v) / (double)ratio;
-    const int64_t by_l2 = std::max<int64_t>(1, (int64_t)(48.0 * 1048576.0 / kv_bytes_per_slab));
+    if (!causal || slabs <= 1) return TX_OK;
+    const int64_t by_l2 = std::max<int64_t>(1, (int64_t)(48.0 * 1048576.0 / bytes_per_slab));
     const int64_t two_waves = (2 * sms + items_per_slab - 1) / items_per_slab;
     const int64_t want = std::min<int64_t>(slabs, std::max(by_l2, two_waves));
     const int64_t n_groups = (slabs + want - 1) / want;
     const int64_t g = (slabs + n_groups - 1) / n_groups;          // equal groups, none left small at the end
-    *group = std::min<int64_t>(slabs, (g + ratio - 1) / ratio * ratio);
+    *group = std::min<int64_t>(slabs, (g + multiple - 1) / multiple * multiple);
     return TX_OK;
+}
+
+int causal_group(const tx_sdpa_desc *d, int64_t items_per_slab, int64_t *group)
+{
+    const int64_t ratio = d->q_heads / d->kv_heads;
+    return launch_group(d->causal != 0, d->batch * d->q_heads, items_per_slab,
+                        2.0 * (double)d->seq_k * (double)(d->d_k + d->d_v) / (double)ratio, ratio, group);
 }
 
 template <class Cfg>
@@ -445,6 +450,8 @@ int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __
     p.causal = d->causal ? 1 : 0;
     p.scale = 1.0f / std::sqrt((float)D);
     p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.group_q = p.group_k = 1;
+    p.items_q = p.items_k = p.slabs_q = p.slabs_k = 1;
     {
         CUtensorMap tq, tdo, tk, tv;
         if (int rc = make_map(&tq, d->q, d->batch * d->q_heads, d->seq_q, D, DqCfg::BM)) return rc;
@@ -453,7 +460,15 @@ int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __
         if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, D, DqCfg::BN)) return rc;
         TX_CUDA(cudaFuncSetAttribute(txb::sdpa_bwd_dq_kernel<DqCfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)DqCfg::SMEM_BYTES));
-        dim3 grid((unsigned)((d->seq_q + DqCfg::BM - 1) / DqCfg::BM), (unsigned)(d->batch * d->q_heads));
+        // 1-D grid, grouped longest-first order for causal calls (a slab's CTAs stream its K and V)
+        const int64_t items = (d->seq_q + DqCfg::BM - 1) / DqCfg::BM, slabs = d->batch * d->q_heads;
+        const int64_t ratio = d->q_heads / d->kv_heads;
+        int64_t group = 1;
+        if (int rc = launch_group(d->causal != 0, slabs, items, 4.0 * (double)d->seq_k * (double)D / (double)ratio, ratio, &group))
+            return rc;
+        p.group_q = (int)group; p.items_q = (int)items; p.slabs_q = (int)slabs;
+        if (items * slabs > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "SDPA backward: more than 2^31 work items");
+        dim3 grid((unsigned)(items * slabs));
         txb::sdpa_bwd_dq_kernel<DqCfg><<<grid, DqCfg::THREADS, DqCfg::SMEM_BYTES, st>>>(tq, tdo, tk, tv, p);
         g_launches++;
         TX_CUDA(cudaGetLastError());
@@ -466,8 +481,16 @@ int launch_bwd(const tx_sdpa_bwd_desc *d, cudaStream_t st, int *status, const __
         if (int rc = make_map(&tv, d->v, d->batch * d->kv_heads, d->seq_k, D, DkvCfg::BMK)) return rc;
         TX_CUDA(cudaFuncSetAttribute(txb::sdpa_bwd_dkv_kernel<DkvCfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)DkvCfg::SMEM_BYTES));
-        dim3 grid((unsigned)((d->seq_k + DkvCfg::BMK - 1) / DkvCfg::BMK), (unsigned)(d->batch * d->kv_heads),
-                  (unsigned)DkvCfg::ZS);
+        // 1-D grid: (slab of (batch, K/V head)) x key tile x column part; a slab's CTAs stream the Q and dO of its
+        // query heads
+        const int64_t items = (d->seq_k + DkvCfg::BMK - 1) / DkvCfg::BMK, slabs = d->batch * d->kv_heads;
+        const int64_t ratio = d->q_heads / d->kv_heads;
+        int64_t group = 1;
+        if (int rc = launch_group(d->causal != 0, slabs, items * DkvCfg::ZS, 4.0 * (double)ratio * (double)d->seq_q * (double)D, 1, &group))
+            return rc;
+        p.group_k = (int)group; p.items_k = (int)items; p.slabs_k = (int)slabs;
+        if (items * slabs * DkvCfg::ZS > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "SDPA backward: more than 2^31 work items");
+        dim3 grid((unsigned)(items * slabs * DkvCfg::ZS));
         txb::sdpa_bwd_dkv_kernel<DkvCfg><<<grid, DkvCfg::THREADS, DkvCfg::SMEM_BYTES, st>>>(tq, tdo, tk, tv, p);
         g_launches++;
         TX_CUDA(cudaGetLastError());

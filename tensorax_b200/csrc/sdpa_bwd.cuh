@@ -40,6 +40,11 @@ struct BwdParams {
     int causal;
     float scale;              // 1/sqrt(d)
     float scale_log2;         // scale * log2(e)
+    // Launch order of the 1-D grids (as in the forward's two-tile kernel): slabs are walked in groups, inside a
+    // group every slab's longest items first.  *_q: the dQ kernel (slab = (batch, query head), item = query tile);
+    // *_k: the dK/dV kernel (slab = (batch, K/V head), item = key tile; its ZS column parts stay side by side).
+    int group_q, items_q, slabs_q;
+    int group_k, items_k, slabs_k;
 };
 
 // ------------------------------------------------------------------ preprocess
@@ -123,9 +128,13 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) causal tiles first
+    // work item: group-major, then longest first over all slabs of the group (late causal query tiles walk most keys)
+    const int span = p.group_q * p.items_q;
+    const int grp = (int)blockIdx.x / span, rem = (int)blockIdx.x % span;
+    const int in_grp = min(p.group_q, p.slabs_q - grp * p.group_q);
+    const int q_tile = p.items_q - 1 - rem / in_grp;
     const int q0 = q_tile * BM;
-    const int bh = blockIdx.y;
+    const int bh = grp * p.group_q + rem % in_grp;
     const int b = bh / p.Hq, h = bh % p.Hq;
     const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
     int kv_limit = p.Sk;
@@ -449,9 +458,15 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::OFF_ABORT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int key0 = (int)blockIdx.x * BMK;
-    const int col0 = (int)blockIdx.z * DA;                      // first dK / dV column of this CTA
-    const int kvh = blockIdx.y;                                 // b * Hkv + kv head
+    // work item: column part fastest, then group-major and longest first over the group's slabs (with a causal
+    // mask the FIRST key tiles are seen by most queries)
+    const int item = (int)blockIdx.x / Cfg::ZS;
+    const int span = p.group_k * p.items_k;
+    const int grp = item / span, rem = item % span;
+    const int in_grp = min(p.group_k, p.slabs_k - grp * p.group_k);
+    const int key0 = (rem / in_grp) * BMK;
+    const int col0 = ((int)blockIdx.x % Cfg::ZS) * DA;          // first dK / dV column of this CTA
+    const int kvh = grp * p.group_k + rem % in_grp;             // b * Hkv + kv head
     const int b = kvh / p.Hkv;
     const int group = p.Hq / p.Hkv;
     const int bh0 = b * p.Hq + (kvh % p.Hkv) * group;           // first query head of the group
