@@ -293,6 +293,8 @@ constexpr int kPolyPairsD64 = 0x0303;
 // back-to-back runs move by 4-5 %: fewer special-function instructions also means a cooler part)
 constexpr int kPolyPairsD128 = 0x0003;
 
+int causal_group(const tx_sdpa_desc *d, int64_t items_per_slab, int64_t *group);
+
 template <class Cfg>
 int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *prof = nullptr)
 {
@@ -318,9 +320,13 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
     p.scale_log2 = (1.0f / std::sqrt((float)d->d_k)) * 1.4426950408889634f;
     p.prof = prof;
     p.skip_k_tile = -1;
+    const int64_t n_tiles = (d->seq_q + Cfg::BM - 1) / Cfg::BM, slabs = d->batch * d->q_heads, zparts = d->d_v / Cfg::DV;
+    int64_t group = 1;
+    if (int rc = causal_group(d, n_tiles * zparts, &group)) return rc;
+    p.group = (int)group; p.n_pairs = (int)n_tiles; p.BH = (int)slabs;
+    if (n_tiles * slabs * zparts > 0x7fffffffLL) return fail(TX_ERR_UNSUPPORTED, "SDPA: more than 2^31 work items");
     if (int rc = allow_smem(txb::sdpa_tc_kernel<Cfg>, (int)Cfg::SMEM_BYTES)) return rc;
-    dim3 grid((unsigned)((d->seq_q + Cfg::BM - 1) / Cfg::BM), (unsigned)(d->batch * d->q_heads),
-              (unsigned)(d->d_v / Cfg::DV));
+    dim3 grid((unsigned)(n_tiles * slabs * zparts), 1, 1);
     txb::sdpa_tc_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, to, p);
     g_launches++;
     TX_CUDA(cudaGetLastError());

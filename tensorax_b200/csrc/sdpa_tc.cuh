@@ -167,7 +167,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // section profile: `tick(i)` adds the cycles since the previous tick to counter i
-    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool prof_on = Cfg::PROF && p.prof != nullptr && blockIdx.x == 0;
     long long prof_last = 0;
     long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     auto tick = [&](int i) {
@@ -184,10 +184,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (prof_on) prof_last = clock64();
         }
     };
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) causal tiles first
+    // Work item of this CTA (1-D grid): the value-column parts of a query tile side by side, then slabs in groups
+    // with every slab's longest items first inside a group (late causal query tiles walk most keys), as in
+    // sdpa_tc_pair_kernel; p.n_pairs counts this kernel's query tiles per slab.
+    const int zparts = p.dv_total / DV;
+    const int item = (int)blockIdx.x / zparts;
+    const int span = p.group * p.n_pairs;
+    const int grp = item / span, rem = item % span;
+    const int in_grp = min(p.group, p.BH - grp * p.group);
+    const int q_tile = p.n_pairs - 1 - rem / in_grp;
     const int q0 = q_tile * BM;
-    const int bh = blockIdx.y;
-    const int dv0 = (int)blockIdx.z * DV;                      // first value column of this CTA
+    const int bh = grp * p.group + rem % in_grp;
+    const int dv0 = ((int)blockIdx.x % zparts) * DV;           // first value column of this CTA
     const int b = bh / p.Hq, h = bh % p.Hq;
     const int kvh = b * p.Hkv + h / (p.Hq / p.Hkv);
 
