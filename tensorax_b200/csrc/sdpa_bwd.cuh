@@ -403,7 +403,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // brings the CTA down to 256 tensor-memory columns at d = 64 so that two CTAs share an SM.
 // NS / NSD: depth of the Q / dO ring; both stages are read twice (K-major for S^T / dP^T, MN-major for
 // dK / dV) and stay occupied until the second read is done.
-// ZS: CTAs (grid.z) that share one key tile, each accumulating D/ZS columns of dK and dV (both form the whole
+// ZS: CTAs (side by side in the 1-D grid) that share one key tile, each accumulating D/ZS columns of dK and dV (both form the whole
 // S^T and dP^T): at d = 256 the two accumulators of one CTA would need all 512 tensor-memory columns.
 template <int D_, int BQ_, int NS_, int WGS_ = 1, bool PS_SMEM_ = false, int NSD_ = NS_, int ZS_ = 1>
 struct BwdDkvCfg {

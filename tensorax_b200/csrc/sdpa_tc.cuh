@@ -46,7 +46,7 @@ struct TcParams {
     const int32_t *kv_lens;   // optional [B]
     int *status;              // device word: 0 = ok, else first failing wait's code
     int Hq, Hkv, Sq, Sk;
-    int dv_total;             // row length of `out` (= DV * gridDim.z)
+    int dv_total;             // row length of `out` (= DV * the CTAs per query tile)
     int causal;
     int out_f16;
     float scale_log2;         // (1/sqrt(d_k)) * log2(e)
