@@ -183,6 +183,11 @@ TX_API int tx_sdpa_finish(void *stream);
 TX_API int tx_sdpa_uses_tensor_cores(const tx_sdpa_desc *desc);
 /* How many kernels of this library have been launched by this process so far. */
 TX_API int64_t tx_kernel_launch_count(void);
+/* Launch order of causal calls (forward and backward): the (batch, head) slabs are walked in equal groups and inside
+ * a group every slab's longest work items come first; a group holds as many slabs as stream `bytes` of K/V (or, in
+ * the dK/dV kernel, Q and dO) through L2 together, at least two waves of CTAs.  Default 48 MiB (bytes <= 0 restores
+ * it).  The order changes when a CTA runs, never what it computes: results are bitwise the same for every value. */
+TX_API int tx_sdpa_set_group_l2_bytes(int64_t bytes);
 
 /* ---- section profiles of the fp32 launchers: reference csrc/tensor_ops.h:214-233
  *      (sdpa_{naive,tiled,flash,mma,optimized_flash}_profile_sections_cuda, bound to Python as

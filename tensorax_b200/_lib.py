@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "tx_sdpa_backward",
     "tx_sdpa_naive_profile_sections_cuda", "tx_sdpa_tiled_profile_sections_cuda", "tx_sdpa_flash_profile_sections_cuda",
     "tx_sdpa_mma_profile_sections_cuda", "tx_sdpa_optimized_flash_profile_sections_cuda",
-    "tx_selftest_wait_timeout", "tx_sdpa_forward_host_copies_only",
+    "tx_selftest_wait_timeout", "tx_sdpa_forward_host_copies_only", "tx_sdpa_set_group_l2_bytes",
 )
 
 
@@ -105,6 +105,7 @@ def load():
     lib.tx_repeat_interleave_cuda.argtypes = [c_void_p, c_void_p] + [c_int64] * 4 + [c_int32]
     lib.tx_linear_f32_cuda.argtypes = [c_void_p] * 4 + [c_int64] * 4 + [c_int32] * 2
     lib.tx_linear_set_cuda_cores_only.argtypes = [c_int]
+    lib.tx_sdpa_set_group_l2_bytes.argtypes = [c_int64]
     lib.tx_sdpa_forward.argtypes = [ctypes.POINTER(SdpaDesc)]
     lib.tx_profile_sections_sdpa.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_longlong)]
     lib.tx_selftest_wait_timeout.argtypes = [ctypes.POINTER(SdpaDesc), c_int32]

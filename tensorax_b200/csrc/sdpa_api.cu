@@ -335,6 +335,8 @@ int launch_tc_t(const tx_sdpa_desc *d, cudaStream_t st, int *status, long long *
 
 // Slabs per group of the launch order of a causal call (see launch_two_tiles); 1 = slab-major.  `bytes_per_slab`: what
 // the CTAs of one slab stream through L2; `multiple`: slabs that share those bytes and should stay together.
+std::atomic<long long> g_group_l2_bytes{48ll << 20};
+
 int launch_group(bool causal, int64_t slabs, int64_t items_per_slab, double bytes_per_slab, int64_t multiple, int64_t *group,
                  int64_t max_waves = 0)
 {
@@ -343,7 +345,7 @@ int launch_group(bool causal, int64_t slabs, int64_t items_per_slab, double byte
     if (int rc = sm_count(&sms)) return rc;
     if (!causal || slabs <= 1) return TX_OK;
     if (max_waves > 0 && items_per_slab * slabs > max_waves * sms) return TX_OK;   // a long launch: its tail is small anyway
-    const int64_t by_l2 = std::max<int64_t>(1, (int64_t)(48.0 * 1048576.0 / bytes_per_slab));
+    const int64_t by_l2 = std::max<int64_t>(1, (int64_t)((double)g_group_l2_bytes.load() / bytes_per_slab));
     const int64_t two_waves = (2 * sms + items_per_slab - 1) / items_per_slab;
     const int64_t want = std::min<int64_t>(slabs, std::max(by_l2, two_waves));
     const int64_t n_groups = (slabs + want - 1) / want;
@@ -1094,6 +1096,12 @@ int tx_repeat_interleave_cuda(const void *in, void *out, int64_t outer, int64_t 
                                                                static_cast<uint32_t *>(out), total, dim_size, inner, repeats);
     g_launches++;
     TX_CUDA(cudaGetLastError());
+    return TX_OK;
+}
+
+int tx_sdpa_set_group_l2_bytes(int64_t bytes)
+{
+    g_group_l2_bytes.store(bytes > 0 ? (long long)bytes : (48ll << 20));
     return TX_OK;
 }
 

@@ -293,3 +293,40 @@ def test_peaked_attention_rows_forward_and_backward(d):
     np.testing.assert_allclose(lse, rl, rtol=2e-5, atol=2e-3)
     for got, r, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
         assert_grad_close(got, r, name)
+
+
+# ------------------------------------------------------------------ launch order
+def test_launch_order_never_changes_a_result():
+    """Causal calls walk their (batch, head) slabs in groups, longest work items first (tx_sdpa_set_group_l2_bytes).
+    A group is never smaller than two waves of CTAs, so the call has many slabs: 117 (batch, query head) slabs of three
+    query pairs fall into two groups of 60 and 57 (whole K/V heads of three query heads each) under a small budget and
+    into one under the default.  Every CTA computes what it always computes:
+    forward (fp16 at d = 64, 128, 256; fp32 on the tensor cores) and backward are bitwise the same either way, and right."""
+    lib = _lib.load()
+    B, Hq, Hkv, S = 3, 39, 13, 700
+    lens = [700, 333, 512]
+    try:
+        for d in (64, 128, 256):
+            q = seeded(500 + d, B, Hq, S, d).astype(np.float16)
+            k, v = (seeded(501 + d + j, B, Hkv, S, d).astype(np.float16) for j in range(2))
+            g = seeded(510 + d, B, Hq, S, d)
+            res = []
+            for budget in (0, 1 << 20, 300 << 10):
+                _lib.check(lib.tx_sdpa_set_group_l2_bytes(budget))
+                res.append(backward_device(q, k, v, g, causal=True, kv_lens=lens))
+            for other in res[1:]:
+                for a, b in zip(res[0], other):
+                    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+            ref = oracle.sdpa_structured(widen(q), widen(k), widen(v), causal=True, kv_lens=lens, threads=8)
+            assert_close_fp16(res[0][0], ref)
+            if d <= 128:
+                q32, k32, v32 = seeded(520 + d, B, Hq, S, d), seeded(521 + d, B, Hkv, S, d), seeded(522 + d, B, Hkv, S, d)
+                outs = []
+                for budget in (0, 1 << 20):
+                    _lib.check(lib.tx_sdpa_set_group_l2_bytes(budget))
+                    o32, tc = sdpa_device(q32, k32, v32, causal=True, kv_lens=lens)
+                    assert tc
+                    outs.append(o32)
+                assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    finally:
+        _lib.check(lib.tx_sdpa_set_group_l2_bytes(0))
